@@ -1,0 +1,95 @@
+/* C ABI of libintra_b200: INTRA forward sparse attention on NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only; no PyTorch or C++ types cross this boundary. Every function
+ * returns an int status (0 = INTRA_OK, negative = rejected before anything was launched, see
+ * intra_b200_strerror) and never throws. Launches are asynchronous on the given CUDA stream.
+ *
+ * Tensors are bf16 with head dim 128, addressed as (batch, token, head, 128) through three element
+ * strides {batch, token, head}; the innermost stride is 1. Base pointers and all strides must keep
+ * every 128-element row 16-byte aligned. q/out have H heads, k/v have Hkv heads, H % Hkv == 0.
+ */
+#ifndef INTRA_B200_H_
+#define INTRA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define INTRA_OK 0
+#define INTRA_ERR_BAD_ARG (-1)      /* null pointer, non-positive size, H % Hkv != 0, bad scale */
+#define INTRA_ERR_UNSUPPORTED (-2)  /* pattern id / group_num / window / width / seqlen combination */
+#define INTRA_ERR_ALIGNMENT (-3)    /* a pointer or stride breaks the 16-byte row alignment */
+#define INTRA_ERR_CUDA (-4)         /* a CUDA runtime call failed; see intra_b200_last_cuda_error */
+#define INTRA_ERR_DEVICE (-5)       /* the device is not an sm_100 part */
+#define INTRA_ERR_KERNEL (-6)       /* a kernel gave up on a bounded wait; see intra_b200_device_status */
+
+/* Pattern ids, identical to the reference's (intra_attn/interface.py:12-13). */
+#define INTRA_LLM_SCATTER 0
+#define INTRA_LLM_GATHER1 1
+#define INTRA_LLM_WINDOW 4
+#define INTRA_IMAGE_SCATTER 0
+#define INTRA_IMAGE_GATHER0 4
+
+/* Causal prefill attention for language models; replaces the reference's `fwd_llm` binding
+ * (csrc/flash_attn/flash_api.cpp:556-763, bound at :1769). `pattern` is INTRA_LLM_*:
+ *   scatter: token i attends j <= i with j % group_num == i % group_num (any S, any group_num <= S)
+ *   gather1: segments of group_num tokens, segment s in group s % group_num (any S, any group_num)
+ *   window:  each 64-query block attends itself and the preceding window-64 tokens (window >= 64)
+ * `window` is ignored by scatter/gather1, `group_num` by window. `out` must not alias q, k or v. */
+int intra_b200_fwd_llm(const void* q, const void* k, const void* v, void* out,
+                       int B, int S, int H, int Hkv,
+                       const int64_t q_strides[3], const int64_t k_strides[3],
+                       const int64_t v_strides[3], const int64_t out_strides[3],
+                       int pattern, int group_num, int window, float softmax_scale,
+                       int device, void* cuda_stream);
+
+/* Bidirectional attention over 512 text tokens followed by a width x width image grid
+ * (S == 512 + width * width, width a multiple of 8, >= 16); replaces the reference's `fwd` binding
+ * (csrc/flash_attn/flash_api.cpp:355-552, bound at :1768). `pattern` is INTRA_IMAGE_*. */
+int intra_b200_fwd_image(const void* q, const void* k, const void* v, void* out,
+                         int B, int S, int H,
+                         const int64_t q_strides[3], const int64_t k_strides[3],
+                         const int64_t v_strides[3], const int64_t out_strides[3],
+                         int pattern, int width, float softmax_scale,
+                         int device, void* cuda_stream);
+
+/* Text for a status code; replaces the reference's TORCH_CHECK messages
+ * (csrc/flash_attn/flash_api.cpp:377-394, 576-597). */
+const char* intra_b200_strerror(int status);
+
+/* cudaError_t of the most recent failed CUDA call made by this library on the calling thread
+ * (0 if none); the counterpart of C10_CUDA_KERNEL_LAUNCH_CHECK
+ * (csrc/flash_attn/src/flash_fwd_launch_template.h:516). */
+int intra_b200_last_cuda_error(void);
+
+/* Synchronises `device` and reads the word its kernels write when a bounded wait runs out
+ * (0 = no kernel has given up since the last reset). `reset` != 0 clears it afterwards. Returns
+ * INTRA_ERR_KERNEL when the word is non-zero. No counterpart in the reference, whose kernels have
+ * no waits that can fail. */
+int intra_b200_device_status(int device, int* status_word, int reset);
+
+/* Test hooks (the reference has no counterpart): the (query, key) pairs the index maps visit.
+ * `family` 0 = llm, 1 = image; `param` = group_num (scatter, gather1), window, or width.
+ * counts is S*S bytes; counts[q*S + k] is incremented once per visit. The host variant evaluates
+ * the maps on the CPU into host memory; the device variant evaluates them in a kernel into device
+ * memory that the caller has zeroed. */
+int intra_b200_visited_host(int family, int pattern, int S, int param, uint8_t* counts);
+int intra_b200_visited_device(int family, int pattern, int S, int param, uint8_t* counts_dev,
+                              int device, void* cuda_stream);
+
+/* Test hook: number of tiles (CTAs per batch and head) and key tiles summed over them, i.e. the
+ * tensor-core work the launch does in units of 128 x 128 score tiles. */
+int intra_b200_tile_counts(int family, int pattern, int S, int param, int64_t* n_tiles, int64_t* n_kv_tiles);
+
+/* Test hook: one 128x128x128 tile through both tensor-core contractions with the attention
+ * kernel's operand layouts. a, b, v: device [128][128] bf16; s_out = a b^T and
+ * o_out = bf16(s_out * p_scale) v, device [128][128] fp32. */
+int intra_b200_selftest_umma(const void* a, const void* b, const void* v, float p_scale,
+                             float* s_out, float* o_out, int device, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INTRA_B200_H_ */

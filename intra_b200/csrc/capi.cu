@@ -1,0 +1,255 @@
+// Host side of libintra_b200: argument checks, per-pattern problem set-up and kernel launches
+// behind the C ABI of include/intra_b200.h. Mirrors what the reference's ATen host code does
+// (csrc/flash_attn/flash_api.cpp:355-552 `mha_fwd`, :556-763 `mha_fwd_llm`) without ATen: the caller
+// owns every tensor, this file only validates, fills the parameter block and launches.
+#include "../../include/intra_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <mutex>
+#include <vector>
+
+#include "attn_kernel.cuh"
+#include "selftest.cuh"
+
+namespace {
+
+using namespace intra;
+
+thread_local int g_last_cuda_error = 0;
+
+constexpr int MAX_DEVICES = 64;
+struct DeviceState {
+  std::once_flag once;
+  int init_status = INTRA_OK;
+  int* status_word = nullptr;     // device memory, one int
+};
+DeviceState g_dev[MAX_DEVICES];
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return INTRA_ERR_CUDA;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+    if (prev != device && cudaSetDevice(device) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+// One-time set-up of a device (current when called): architecture check, shared-memory opt-in of the
+// kernels, and the status word the kernels report to.
+void init_device(int device) {
+  DeviceState& st = g_dev[device];
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) { st.init_status = cuda_fail(e); return; }
+  if (prop.major != 10) { st.init_status = INTRA_ERR_DEVICE; return; }
+  e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaMalloc(&st.status_word, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(st.status_word, 0, sizeof(int));
+  if (e != cudaSuccess) st.init_status = cuda_fail(e);
+}
+
+int ensure_device(int device) {
+  if (device < 0 || device >= MAX_DEVICES) return INTRA_ERR_BAD_ARG;
+  DeviceState& st = g_dev[device];
+  std::call_once(st.once, init_device, device);
+  return st.init_status;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool strides_ok(const int64_t s[3]) { return s && s[0] % 8 == 0 && s[1] % 8 == 0 && s[2] % 8 == 0; }
+
+int map_kind(int family, int pattern) {
+  if (family == 0) {
+    if (pattern == INTRA_LLM_SCATTER) return KIND_LLM_SCATTER;
+    if (pattern == INTRA_LLM_GATHER1) return KIND_LLM_GATHER1;
+    if (pattern == INTRA_LLM_WINDOW) return KIND_LLM_WINDOW;
+  } else if (family == 1) {
+    if (pattern == INTRA_IMAGE_SCATTER) return KIND_IMG_SCATTER;
+    if (pattern == INTRA_IMAGE_GATHER0) return KIND_IMG_GATHER0;
+  }
+  return -1;
+}
+
+// `param` is group_num for scatter / gather1 and window / width otherwise.
+int problem_from(int family, int pattern, int S, int param, Problem* prob) {
+  const int kind = map_kind(family, pattern);
+  if (kind < 0) return INTRA_ERR_UNSUPPORTED;
+  const bool grouped = kind == KIND_LLM_SCATTER || kind == KIND_LLM_GATHER1;
+  if (make_problem(kind, S, grouped ? param : 0, grouped ? 0 : param, prob) != 0) return INTRA_ERR_UNSUPPORTED;
+  return INTRA_OK;
+}
+
+int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, int S, int H, int Hkv,
+               const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, int family, int pattern,
+               int param, float softmax_scale, int device, void* stream) {
+  if (!q || !k || !v || !out || B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0) return INTRA_ERR_BAD_ARG;
+  if (!qs || !ks || !vs || !os) return INTRA_ERR_BAD_ARG;
+  if (!(softmax_scale > 0.f) || !std::isfinite(softmax_scale)) return INTRA_ERR_BAD_ARG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !strides_ok(qs) || !strides_ok(ks) ||
+      !strides_ok(vs) || !strides_ok(os))
+    return INTRA_ERR_ALIGNMENT;
+  FwdParams p;
+  int rc = problem_from(family, pattern, S, param, &p.prob);
+  if (rc != INTRA_OK) return rc;
+  const int64_t blocks = int64_t(p.prob.n_tiles) * B * H;
+  if (blocks <= 0 || blocks > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
+
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  rc = ensure_device(device);
+  if (rc != INTRA_OK) return rc;
+
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k = static_cast<const __nv_bfloat16*>(k);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.o = static_cast<__nv_bfloat16*>(out);
+  p.qs = {qs[0], qs[1], qs[2]};
+  p.ks = {ks[0], ks[1], ks[2]};
+  p.vs = {vs[0], vs[1], vs[2]};
+  p.os = {os[0], os[1], os[2]};
+  p.B = B; p.H = H; p.Hkv = Hkv;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = g_dev[device].status_word;
+  intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return INTRA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int intra_b200_fwd_llm(const void* q, const void* k, const void* v, void* out, int B, int S, int H, int Hkv,
+                       const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                       const int64_t out_strides[3], int pattern, int group_num, int window, float softmax_scale,
+                       int device, void* cuda_stream) {
+  const int param = pattern == INTRA_LLM_WINDOW ? window : group_num;
+  return launch_fwd(q, k, v, out, B, S, H, Hkv, q_strides, k_strides, v_strides, out_strides, 0, pattern, param,
+                    softmax_scale, device, cuda_stream);
+}
+
+int intra_b200_fwd_image(const void* q, const void* k, const void* v, void* out, int B, int S, int H,
+                         const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                         const int64_t out_strides[3], int pattern, int width, float softmax_scale, int device,
+                         void* cuda_stream) {
+  return launch_fwd(q, k, v, out, B, S, H, H, q_strides, k_strides, v_strides, out_strides, 1, pattern, width,
+                    softmax_scale, device, cuda_stream);
+}
+
+const char* intra_b200_strerror(int status) {
+  switch (status) {
+    case INTRA_OK: return "ok";
+    case INTRA_ERR_BAD_ARG: return "bad argument: null pointer, non-positive size, heads not divisible, or softmax scale not positive";
+    case INTRA_ERR_UNSUPPORTED: return "unsupported pattern / group_num / window / width / sequence length";
+    case INTRA_ERR_ALIGNMENT: return "pointers and strides must keep every 128-element bf16 row 16-byte aligned";
+    case INTRA_ERR_CUDA: return "a CUDA runtime call failed (see intra_b200_last_cuda_error)";
+    case INTRA_ERR_DEVICE: return "device is not an sm_100 (B200) GPU";
+    case INTRA_ERR_KERNEL: return "a kernel gave up on a bounded wait (see intra_b200_device_status)";
+    default: return "unknown status";
+  }
+}
+
+int intra_b200_last_cuda_error(void) { return g_last_cuda_error; }
+
+int intra_b200_device_status(int device, int* status_word, int reset) {
+  if (!status_word) return INTRA_ERR_BAD_ARG;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  int rc = ensure_device(device);
+  if (rc != INTRA_OK) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(status_word, g_dev[device].status_word, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && reset && *status_word != 0) e = cudaMemset(g_dev[device].status_word, 0, sizeof(int));
+  if (e != cudaSuccess) return cuda_fail(e);
+  return *status_word == 0 ? INTRA_OK : INTRA_ERR_KERNEL;
+}
+
+int intra_b200_visited_host(int family, int pattern, int S, int param, uint8_t* counts) {
+  if (!counts) return INTRA_ERR_BAD_ARG;
+  Problem prob;
+  int rc = problem_from(family, pattern, S, param, &prob);
+  if (rc != INTRA_OK) return rc;
+  for (int idx = 0; idx < prob.n_tiles; ++idx) {
+    const Tile t = make_tile(prob, idx);
+    if (t.n_kv_tiles == 0) continue;
+    for (int r = 0; r < TILE_M; ++r) {
+      int token, lo, hi;
+      q_row(prob, t, r, &token, &lo, &hi);
+      if (token < 0) continue;
+      if (token >= S || lo < 0 || hi >= t.n_kv_tiles * TILE_N) return INTRA_ERR_KERNEL;   // map out of range
+      for (int u = lo; u <= hi; ++u) {
+        const int kt = key_token(prob, t, u);
+        if (kt < 0) continue;
+        if (kt >= S) return INTRA_ERR_KERNEL;
+        uint8_t* c = counts + size_t(token) * S + kt;
+        if (*c < 255) ++*c;
+      }
+    }
+  }
+  return INTRA_OK;
+}
+
+int intra_b200_visited_device(int family, int pattern, int S, int param, uint8_t* counts_dev, int device,
+                              void* cuda_stream) {
+  if (!counts_dev) return INTRA_ERR_BAD_ARG;
+  Problem prob;
+  int rc = problem_from(family, pattern, S, param, &prob);
+  if (rc != INTRA_OK) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  rc = ensure_device(device);
+  if (rc != INTRA_OK) return rc;
+  visited_kernel<<<prob.n_tiles, TILE_M, 0, static_cast<cudaStream_t>(cuda_stream)>>>(prob, counts_dev);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
+}
+
+int intra_b200_tile_counts(int family, int pattern, int S, int param, int64_t* n_tiles, int64_t* n_kv_tiles) {
+  if (!n_tiles || !n_kv_tiles) return INTRA_ERR_BAD_ARG;
+  Problem prob;
+  int rc = problem_from(family, pattern, S, param, &prob);
+  if (rc != INTRA_OK) return rc;
+  int64_t nt = 0, nkv = 0;
+  for (int idx = 0; idx < prob.n_tiles; ++idx) {
+    const Tile t = make_tile(prob, idx);
+    if (t.n_kv_tiles == 0) continue;
+    ++nt;
+    nkv += t.n_kv_tiles;
+  }
+  *n_tiles = nt;
+  *n_kv_tiles = nkv;
+  return INTRA_OK;
+}
+
+int intra_b200_selftest_umma(const void* a, const void* b, const void* v, float p_scale, float* s_out, float* o_out,
+                             int device, void* cuda_stream) {
+  if (!a || !b || !v || !s_out || !o_out) return INTRA_ERR_BAD_ARG;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  int rc = ensure_device(device);
+  if (rc != INTRA_OK) return rc;
+  umma_selftest_kernel<<<1, 128, FWD_SMEM_BYTES, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
+      static_cast<const __nv_bfloat16*>(v), p_scale, s_out, o_out, g_dev[device].status_word);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
+}
+
+}  // extern "C"

@@ -1,0 +1,126 @@
+"""Python entry points, drop-in for the reference's `intra_attn/interface.py`.
+
+Same names, defaults, argument meaning and exceptions as the reference
+(intra_attn/interface.py:17-66); the work is done by libintra_b200.so through its C ABI.
+All functions take q, k, v of shape (batch, seqlen, heads, 128) in bfloat16 on a B200 and return the
+attention output shaped, typed and laid out like q. k/v may have fewer heads than q (GQA) as long as
+they divide the query heads. Forward only.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _loader
+from ._loader import lib, strides3
+
+LLM_PATTERNS = {"scatter": 0, "gather1": 1, "window": 4}
+IMAGE_PATTERNS = {"scatter": 0, "gather0": 4}
+TEXT_LEN = 512
+
+
+def _check(q, k, v):
+    """Argument checks of the reference (intra_attn/interface.py:17-23), plus the layout the
+    library needs: the reference's kernels silently assume 128-element head stride and equal q/k row
+    strides; here any batch/token/head strides are honoured as long as rows stay 16-byte aligned,
+    and tensors that break that are made contiguous first."""
+    for x in (q, k, v):
+        if not x.is_cuda or x.dtype != torch.bfloat16 or x.shape[-1] != 128:
+            raise ValueError("INTRA kernels need CUDA bfloat16 tensors with head_dim 128")
+    if torch.is_grad_enabled() and any(x.requires_grad for x in (q, k, v)):
+        raise RuntimeError("INTRA kernels are forward-only; call them under torch.no_grad()")
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q, k, v must be (batch, seqlen, heads, 128)")
+    if k.shape != v.shape or k.shape[:2] != q.shape[:2] or q.shape[2] % k.shape[2] != 0:
+        raise ValueError(f"incompatible shapes q={tuple(q.shape)} k={tuple(k.shape)} v={tuple(v.shape)}")
+    if k.device != q.device or v.device != q.device:
+        raise ValueError("q, k, v must be on the same device")
+
+    def usable(x):
+        return (x.stride(-1) == 1 and x.data_ptr() % 16 == 0
+                and all(x.stride(d) % 8 == 0 for d in range(3)))
+
+    return [x if usable(x) else x.contiguous() for x in (q, k, v)]
+
+
+def _scale(q, softmax_scale):
+    return q.shape[-1] ** -0.5 if softmax_scale is None else float(softmax_scale)
+
+
+def _raise(status):
+    msg = _loader.strerror(status)
+    if status == _loader.ERR_CUDA:
+        raise RuntimeError(f"intra_b200: {msg} (cudaError {lib.intra_b200_last_cuda_error()})")
+    if status in (_loader.ERR_DEVICE, _loader.ERR_KERNEL):
+        raise RuntimeError(f"intra_b200: {msg}")
+    raise ValueError(f"intra_b200: {msg}")
+
+
+def _empty_like(q):
+    out = torch.empty_like(q)
+    if out.stride(-1) != 1 or any(out.stride(d) % 8 for d in range(3)):
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    return out
+
+
+def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_scale=None):
+    """Causal prefill attention for language models.
+
+    pattern="scatter": token i attends to earlier tokens j with j % group_num == i % group_num.
+    pattern="gather1": groups are segments of group_num tokens, segment s in group s % group_num.
+    pattern="window":  each 64-query block attends to itself and the preceding window - 64 tokens.
+
+    Any seqlen works for scatter and window; gather1 keeps the reference's contract of
+    group_num=8 and seqlen % 64 == 0 (intra_attn/interface.py:41-42).
+    """
+    q, k, v = _check(q, k, v)
+    if pattern == "gather1" and (group_num != 8 or q.shape[1] % (group_num * group_num)):
+        raise ValueError(f"gather1 needs group_num=8 and seqlen % 64 == 0, got G={group_num}, S={q.shape[1]}")
+    pid = LLM_PATTERNS[pattern]
+    out = _empty_like(q)
+    B, S, H, _ = q.shape
+    rc = lib.intra_b200_fwd_llm(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H, k.shape[2],
+                                strides3(q), strides3(k), strides3(v), strides3(out), pid, int(group_num),
+                                int(window), _scale(q, softmax_scale), q.device.index,
+                                torch.cuda.current_stream(q.device).cuda_stream)
+    if rc != 0:
+        _raise(rc)
+    return out
+
+
+def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None):
+    """Bidirectional attention for FLUX-style sequences: 512 text tokens followed by a
+    width x width grid of image tokens.
+
+    pattern="scatter": 8 groups, image token (r, c) in group (r % 2) * 4 + c % 4; text chunks of
+                       64 tokens ride with groups 0..7; all text keys are always visible.
+    pattern="gather0": each 8 x 8 image patch attends to a 16 x 16 window around it plus all text.
+
+    width must be 64 or 128 as in the reference (intra_attn/interface.py:60-63).
+    """
+    q, k, v = _check(q, k, v)
+    if width not in (64, 128):
+        raise ValueError("image kernels are compiled for width 64 and 128")
+    if q.shape[1] != TEXT_LEN + width * width:
+        raise ValueError(f"expected {TEXT_LEN} text + {width}x{width} image tokens, got {q.shape[1]}")
+    if k.shape[2] != q.shape[2]:
+        raise ValueError("image attention is multi-head: k/v need as many heads as q")
+    pid = IMAGE_PATTERNS[pattern]
+    out = _empty_like(q)
+    B, S, H, _ = q.shape
+    rc = lib.intra_b200_fwd_image(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H,
+                                  strides3(q), strides3(k), strides3(v), strides3(out), pid, int(width),
+                                  _scale(q, softmax_scale), q.device.index,
+                                  torch.cuda.current_stream(q.device).cuda_stream)
+    if rc != 0:
+        _raise(rc)
+    return out
+
+
+def device_status(device=None, reset=False):
+    """Synchronise `device` and return the status word its kernels write when a bounded wait gives
+    up (0 = healthy). Raises nothing; callers decide."""
+    import ctypes
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    word = ctypes.c_int(0)
+    lib.intra_b200_device_status(dev, ctypes.byref(word), 1 if reset else 0)
+    return word.value

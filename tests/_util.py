@@ -1,0 +1,96 @@
+"""Helpers shared by the tests: golden fixtures, direct C-ABI calls, oracle comparisons."""
+import ctypes
+import json
+import os
+
+import numpy as np
+import torch
+
+from oracle import intra_oracle as oracle
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+ATOL = 1.6e-2   # max-abs bound of the reference on bf16 outputs (README.md:68-69 of the reference)
+
+FAMILY = {"llm": 0, "image": 1}
+PATTERN_ID = {("llm", "scatter"): 0, ("llm", "gather1"): 1, ("llm", "window"): 4,
+              ("image", "scatter"): 0, ("image", "gather0"): 4}
+
+
+def load_mask_goldens():
+    with open(os.path.join(GOLDEN, "masks.json")) as f:
+        return json.load(f)
+
+
+def load_attention_goldens():
+    z = np.load(os.path.join(GOLDEN, "attention.npz"))
+    meta = json.loads(bytes(z["meta"]).decode())
+    return meta, z
+
+
+def case_kwargs(case):
+    return {k: case[k] for k in ("group_num", "window", "width") if k in case}
+
+
+def case_param(case):
+    if case["family"] == "image":
+        return case["width"]
+    return case["window"] if case["pattern"] == "window" else case["group_num"]
+
+
+def case_id(case):
+    return "-".join(str(case[k]) for k in ("family", "pattern", "S", "group_num", "window", "width") if k in case)
+
+
+def bf16_from_bits(bits):
+    return torch.from_numpy(bits.astype(np.int16)).view(torch.bfloat16)
+
+
+def strides3(t):
+    return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def call_fwd(lib, family, pattern, q, k, v, param, scale=None, out=None):
+    """Launch through the C ABI on q's device/current stream; returns (status, out)."""
+    B, S, H, D = q.shape
+    if out is None:
+        out = torch.empty_like(q)
+    scale = D ** -0.5 if scale is None else scale
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    pid = PATTERN_ID[(family, pattern)]
+    if family == "llm":
+        g = param if pattern != "window" else 8
+        w = param if pattern == "window" else 576
+        rc = lib.intra_b200_fwd_llm(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H, k.shape[2],
+                                    strides3(q), strides3(k), strides3(v), strides3(out), pid, g, w, scale,
+                                    q.device.index, stream)
+    else:
+        rc = lib.intra_b200_fwd_image(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H,
+                                      strides3(q), strides3(k), strides3(v), strides3(out), pid, param, scale,
+                                      q.device.index, stream)
+    return rc, out
+
+
+def device_status(lib, device=0, reset=True):
+    word = ctypes.c_int(0)
+    lib.intra_b200_device_status(device, ctypes.byref(word), 1 if reset else 0)
+    return word.value
+
+
+def oracle_attention(q, k, v, mask, scale=None, on_device=False):
+    """fp32 dense-mask oracle. On the CPU by default; with on_device=True the same function runs on
+    q's device one KV-head group at a time (as the reference's kernel test does for long S)."""
+    if not on_device:
+        return oracle.masked_attention(q.cpu(), k.cpu(), v.cpu(), mask, scale)
+    m = torch.from_numpy(np.ascontiguousarray(mask)).to(q.device) if not torch.is_tensor(mask) else mask.to(q.device)
+    H, Hkv = q.shape[2], k.shape[2]
+    rep = H // Hkv
+    out = torch.empty_like(q)
+    for b in range(q.shape[0]):
+        for g in range(Hkv):
+            out[b:b + 1, :, g * rep:(g + 1) * rep] = oracle.masked_attention(
+                q[b:b + 1, :, g * rep:(g + 1) * rep], k[b:b + 1, :, g:g + 1], v[b:b + 1, :, g:g + 1], m, scale)
+    return out
+
+
+def max_abs_err(a, b):
+    return (a.float().cpu() - b.float().cpu()).abs().max().item()

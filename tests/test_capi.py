@@ -1,0 +1,83 @@
+"""The C-ABI library loads, exports every symbol the public header declares, and rejects bad
+arguments before touching a GPU."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from tests import _util
+
+HEADER = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "intra_b200.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(intra_b200_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    from intra_b200 import _loader
+    names = declared_symbols()
+    assert len(names) >= 8
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/intra_b200.h but not exported"
+        assert name in _loader.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_loader.SIGNATURES) == names
+
+
+def test_strerror(lib):
+    assert lib.intra_b200_strerror(0) == b"ok"
+    for code in range(-6, 0):
+        assert len(lib.intra_b200_strerror(code)) > 10
+    assert lib.intra_b200_strerror(-99) == b"unknown status"
+
+
+def test_bad_arguments_are_rejected_without_a_gpu(lib):
+    q = torch.zeros(1, 256, 2, 128, dtype=torch.bfloat16)
+    s = _util.strides3(q)
+    ptr = q.data_ptr()
+    args = lambda **kw: dict(dict(q=ptr, k=ptr, v=ptr, out=ptr, B=1, S=256, H=2, Hkv=1, pattern=0, G=8, W=576,
+                                  scale=0.088), **kw)
+
+    def call(a):
+        return lib.intra_b200_fwd_llm(a["q"], a["k"], a["v"], a["out"], a["B"], a["S"], a["H"], a["Hkv"], s, s, s, s,
+                                      a["pattern"], a["G"], a["W"], a["scale"], 0, None)
+
+    assert call(args(q=None)) == -1
+    assert call(args(S=0)) == -1
+    assert call(args(H=3, Hkv=2)) == -1
+    assert call(args(scale=0.0)) == -1
+    assert call(args(scale=float("nan"))) == -1
+    assert call(args(pattern=7)) == -2
+    assert call(args(pattern=4, W=63)) == -2
+    assert call(args(G=0)) == -2
+    assert call(args(q=ptr + 2)) == -3
+    bad = (ctypes.c_int64 * 3)(q.stride(0), q.stride(1) + 4, q.stride(2))
+    assert lib.intra_b200_fwd_llm(ptr, ptr, ptr, ptr, 1, 256, 2, 1, bad, s, s, s, 0, 8, 576, 0.088, 0, None) == -3
+    assert lib.intra_b200_fwd_image(ptr, ptr, ptr, ptr, 1, 256, 2, s, s, s, s, 0, 64, 0.088, 0, None) == -2
+    assert lib.intra_b200_fwd_image(ptr, ptr, ptr, ptr, 1, 512 + 4096, 2, s, s, s, s, 1, 64, 0.088, 0, None) == -2
+
+
+def test_python_entry_points_validate_like_the_reference():
+    from intra_b200 import intra_image_attn, intra_llm_attn
+    q = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA bfloat16"):
+        intra_llm_attn(q, q, q)
+    with pytest.raises(ValueError, match="CUDA bfloat16"):
+        intra_image_attn(q, q, q)
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="only meaningful on a machine without a GPU")
+def test_no_cpu_fallback(lib):
+    """Without a GPU a well-formed call must fail with a CUDA error status, never compute."""
+    q = torch.zeros(1, 256, 2, 128, dtype=torch.bfloat16)
+    s = _util.strides3(q)
+    out = torch.full_like(q, 7.0)
+    rc = lib.intra_b200_fwd_llm(q.data_ptr(), q.data_ptr(), q.data_ptr(), out.data_ptr(), 1, 256, 2, 2, s, s, s, s,
+                                0, 8, 576, 0.088, 0, None)
+    assert rc in (-4, -5)
+    assert bool((out == 7.0).all())

@@ -1,0 +1,51 @@
+"""The CPU oracle against the fixtures generated from the reference's own Python code."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import intra_oracle as oracle
+from tests import _util
+
+MASK_CASES = _util.load_mask_goldens()
+ATTN_META, ATTN = _util.load_attention_goldens()
+
+
+@pytest.mark.parametrize("case", MASK_CASES, ids=_util.case_id)
+def test_mask_matches_reference_digest(case):
+    m = oracle.build_mask(case["family"], case["pattern"], case["S"], **_util.case_kwargs(case))
+    d = oracle.mask_digest(m)
+    assert d["shape"] == case["shape"]
+    assert d["pairs"] == case["pairs"]
+    assert d["row_checksum"] == case["row_checksum"]
+    assert d["sha256"] == case["sha256"]
+    assert oracle.pair_count(case["family"], case["pattern"], case["S"], **_util.case_kwargs(case)) == case["pairs"]
+
+
+def test_pair_counts_at_benchmark_sizes():
+    # Closed forms at sizes whose dense masks are too large to build in a unit test.
+    assert oracle.pair_count("llm", "scatter", 4096, group_num=8) == 1050624
+    assert oracle.pair_count("llm", "gather1", 16384, group_num=8) == 16785408
+    assert oracle.pair_count("llm", "window", 16384, window=576) == 8773632
+    assert oracle.pair_count("llm", "scatter", 65536, group_num=8) == 268468224
+    assert oracle.pair_count("llm", "window", 65536, window=576) == 35536896
+    assert oracle.pair_count("llm", "scatter", 32768, group_num=2) == 268451840
+    assert oracle.pair_count("image", "scatter", 512 + 128 * 128, width=128) == 43253760
+    assert oracle.pair_count("image", "gather0", 512 + 128 * 128, width=128) == 13893632
+
+
+@pytest.mark.parametrize("meta", ATTN_META, ids=lambda m: m["name"])
+def test_attention_matches_reference_output(meta):
+    q, k, v = oracle.make_inputs(meta["B"], meta["S"], meta["H"], meta["Hkv"], seed=meta["seed"])
+    h = hashlib.sha256()
+    for x in (q, k, v):
+        h.update(x.contiguous().view(torch.int16).numpy().view(np.uint16).tobytes())
+    assert h.hexdigest() == meta["inputs_sha256"], "seeded inputs differ from the ones the fixture was made with"
+    mask = oracle.build_mask(meta["family"], meta["pattern"], meta["S"], **_util.case_kwargs(meta))
+    want = _util.bf16_from_bits(ATTN[meta["name"]])
+    got = oracle.masked_attention(q, k, v, mask)
+    # Same algorithm as the fixture's generator; one bf16 ulp of slack for a different CPU's SDPA.
+    assert torch.allclose(got.float(), want.float(), atol=2e-3, rtol=8e-3)
+    rows = oracle.masked_attention_rows(q, k, v, mask, rows=200)
+    assert torch.allclose(rows.float(), want.float(), atol=2e-3, rtol=8e-3)

@@ -1,0 +1,203 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the oracle and the golden fixtures."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import intra_oracle as oracle
+from tests import _util
+
+pytestmark = pytest.mark.gpu
+
+MASK_CASES = _util.load_mask_goldens()
+ATTN_META, ATTN = _util.load_attention_goldens()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(lib):
+    """Every test starts and ends with a healthy device status word."""
+    assert torch.cuda.is_available()
+    _util.device_status(lib, 0, reset=True)
+    yield
+    assert _util.device_status(lib, 0, reset=True) == 0, "a kernel gave up on a bounded wait"
+
+
+def test_library_is_native(lib):
+    """The tests must exercise the in-tree CUDA library, on an sm_100 device."""
+    from intra_b200 import _loader
+    assert _loader.LIB_PATH.endswith("intra_b200/_lib/libintra_b200.so")
+    assert torch.cuda.get_device_capability(0)[0] == 10
+
+
+def test_umma_single_tile(lib):
+    """One 128x128x128 tile through both tensor-core contractions (operand layouts, descriptors,
+    TMEM load/store paths) against fp32 matmuls of the same bf16 data."""
+    g = torch.Generator().manual_seed(5)
+    a, b, v = (torch.randn(128, 128, generator=g).to(torch.bfloat16).cuda() for _ in range(3))
+    s_out = torch.zeros(128, 128, device="cuda")
+    o_out = torch.zeros(128, 128, device="cuda")
+    p_scale = 1.0 / 16
+    rc = lib.intra_b200_selftest_umma(a.data_ptr(), b.data_ptr(), v.data_ptr(), p_scale, s_out.data_ptr(),
+                                      o_out.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    s_ref = a.float() @ b.float().t()
+    assert torch.allclose(s_out, s_ref, atol=1e-3, rtol=1e-4)
+    p_ref = (s_out * p_scale).to(torch.bfloat16).float()
+    o_ref = p_ref @ v.float()
+    assert torch.allclose(o_out, o_ref, atol=2e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("case", [c for c in MASK_CASES if c["S"] <= 8192], ids=_util.case_id)
+def test_device_visited_set_equals_mask(lib, case):
+    """The index maps as the device evaluates them: visited (query, key) pairs == oracle mask."""
+    S = case["S"]
+    counts = torch.zeros(S, S, dtype=torch.uint8, device="cuda")
+    rc = lib.intra_b200_visited_device(_util.FAMILY[case["family"]],
+                                       _util.PATTERN_ID[(case["family"], case["pattern"])], S,
+                                       _util.case_param(case), counts.data_ptr(), 0,
+                                       torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    mask = oracle.build_mask(case["family"], case["pattern"], S, **_util.case_kwargs(case))
+    got = counts.cpu().numpy()
+    assert got.max() <= 1
+    assert np.array_equal(got.view(bool), mask)
+
+
+@pytest.mark.parametrize("meta", ATTN_META, ids=lambda m: m["name"])
+def test_golden_outputs(lib, meta):
+    """Outputs of the reference's own oracle on seeded inputs (committed fixtures)."""
+    q, k, v = oracle.make_inputs(meta["B"], meta["S"], meta["H"], meta["Hkv"], seed=meta["seed"], device="cuda")
+    rc, out = _util.call_fwd(lib, meta["family"], meta["pattern"], q, k, v, _util.case_param(meta))
+    assert rc == 0
+    torch.cuda.synchronize()
+    want = _util.bf16_from_bits(ATTN[meta["name"]])
+    assert bool(torch.isfinite(out).all())
+    assert _util.max_abs_err(out, want) <= _util.ATOL
+
+
+def _llm_matrix():
+    cases = []
+    for S in (1000, 2048, 3000, 4096, 8192, 16384):
+        for B, H, Hkv in ((1, 32, 8), (2, 32, 32)):
+            for G in (2, 3, 8):
+                cases.append(("scatter", S, B, H, Hkv, G))
+            if S % 64 == 0:
+                cases.append(("gather1", S, B, H, Hkv, 8))
+            for W in (576, 1000):
+                cases.append(("window", S, B, H, Hkv, W))
+    return cases
+
+
+@pytest.mark.parametrize("pattern,S,B,H,Hkv,param", _llm_matrix(),
+                         ids=lambda x: str(x))
+def test_llm_matrix(lib, pattern, S, B, H, Hkv, param):
+    """The shape matrix of the reference's kernel test (tests/test_kernel.py:33-44), seed 0."""
+    q, k, v = oracle.make_inputs(B, S, H, Hkv, seed=0, device="cuda")
+    rc, out = _util.call_fwd(lib, "llm", pattern, q, k, v, param)
+    assert rc == 0
+    kw = {"window": param} if pattern == "window" else {"group_num": param}
+    mask = oracle.build_mask("llm", pattern, S, **kw)
+    ref = _util.oracle_attention(q, k, v, mask, on_device=True)
+    assert bool(torch.isfinite(out).all())
+    assert _util.max_abs_err(out, ref) <= _util.ATOL
+
+
+@pytest.mark.parametrize("width,H", [(64, 24), (128, 8)])
+@pytest.mark.parametrize("B", [1, 2])
+@pytest.mark.parametrize("pattern", ["scatter", "gather0"])
+def test_image_matrix(lib, pattern, B, width, H):
+    """Image shapes of the reference's kernel test (tests/test_kernel.py:45-51)."""
+    S = 512 + width * width
+    q, k, v = oracle.make_inputs(B, S, H, H, seed=0, device="cuda")
+    rc, out = _util.call_fwd(lib, "image", pattern, q, k, v, width)
+    assert rc == 0
+    mask = oracle.build_mask("image", pattern, S, width=width)
+    ref = _util.oracle_attention(q, k, v, mask, on_device=True)
+    assert bool(torch.isfinite(out).all())
+    assert _util.max_abs_err(out, ref) <= _util.ATOL
+
+
+@pytest.mark.parametrize("family,pattern,S,param", [
+    ("llm", "scatter", 1111, 5), ("llm", "gather1", 777, 4), ("llm", "gather1", 1000, 8),
+    ("llm", "window", 130, 64), ("llm", "window", 129, 200), ("llm", "scatter", 1, 1),
+    ("image", "scatter", 512 + 24 * 24, 24), ("image", "gather0", 512 + 24 * 24, 24),
+    ("image", "gather0", 512 + 40 * 40, 40)])
+def test_ragged_and_small_shapes_vs_cpu_oracle(lib, family, pattern, S, param):
+    """Shapes beyond the reference's restrictions; oracle on the CPU."""
+    H, Hkv = (4, 2) if family == "llm" else (2, 2)
+    q, k, v = oracle.make_inputs(1, S, H, Hkv, seed=3, device="cuda")
+    rc, out = _util.call_fwd(lib, family, pattern, q, k, v, param, scale=0.11)
+    assert rc == 0
+    kw = {"width": param} if family == "image" else ({"window": param} if pattern == "window" else {"group_num": param})
+    mask = oracle.build_mask(family, pattern, S, **kw)
+    ref = _util.oracle_attention(q, k, v, mask, scale=0.11)
+    assert bool(torch.isfinite(out).all())
+    assert _util.max_abs_err(out, ref) <= _util.ATOL
+
+
+def test_python_api_strided_views_and_errors(lib):
+    """The reference-shaped Python API: transposed (B, H, S, D)-storage views as the FLUX caller
+    passes them (experiments/flux/intra_processor.py:128-135), canary rows, run-twice determinism,
+    and the reference's exceptions."""
+    from intra_b200 import intra_image_attn, intra_llm_attn
+    B, S, H, Hkv = 1, 2048, 8, 2
+    g = torch.Generator().manual_seed(9)
+    qs = torch.randn(B, H, S + 2, 128, generator=g).to(torch.bfloat16).cuda()
+    ks = torch.randn(B, Hkv, S + 2, 128, generator=g).to(torch.bfloat16).cuda()
+    vs = torch.randn(B, Hkv, S + 2, 128, generator=g).to(torch.bfloat16).cuda()
+    qs[:, :, 0] = float("nan"); qs[:, :, -1] = float("nan")        # guard rows around the views
+    ks[:, :, 0] = float("nan"); ks[:, :, -1] = float("nan")
+    vs[:, :, 0] = float("nan"); vs[:, :, -1] = float("nan")
+    q, k, v = (x[:, :, 1:-1].transpose(1, 2) for x in (qs, ks, vs))
+    assert not q.is_contiguous() and q.stride(-1) == 1
+    with torch.no_grad():
+        out1 = intra_llm_attn(q, k, v, "scatter", group_num=8)
+        out2 = intra_llm_attn(q, k, v, "scatter", group_num=8)
+        outw = intra_llm_attn(q, k, v, "window", window=576)
+    assert out1.shape == q.shape and out1.dtype == q.dtype
+    assert torch.equal(out1, out2), "two runs differ bitwise"
+    ref = _util.oracle_attention(q, k, v, oracle.llm_scatter_mask(S, 8), on_device=True)
+    assert _util.max_abs_err(out1, ref) <= _util.ATOL
+    refw = _util.oracle_attention(q, k, v, oracle.llm_window_mask(S, 576), on_device=True)
+    assert _util.max_abs_err(outw, refw) <= _util.ATOL
+
+    width = 64
+    Si = 512 + width * width
+    qi = torch.randn(1, 2, Si, 128, generator=g).to(torch.bfloat16).cuda().transpose(1, 2)
+    with torch.no_grad():
+        oi = intra_image_attn(qi, qi, qi, "gather0", width)
+    refi = _util.oracle_attention(qi, qi, qi, oracle.image_gather0_mask(width), on_device=True)
+    assert _util.max_abs_err(oi, refi) <= _util.ATOL
+
+    x = torch.zeros(1, 256, 2, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        intra_llm_attn(x.float(), x.float(), x.float())
+    with pytest.raises(ValueError):
+        intra_llm_attn(x[..., :64], x[..., :64], x[..., :64])
+    with pytest.raises(ValueError, match="gather1"):
+        intra_llm_attn(x, x, x, "gather1", group_num=4)
+    with pytest.raises(ValueError, match="gather1"):
+        intra_llm_attn(x[:, :200], x[:, :200], x[:, :200], "gather1", group_num=8)
+    with pytest.raises(KeyError):
+        intra_llm_attn(x, x, x, "nope")
+    with pytest.raises(ValueError, match="width"):
+        intra_image_attn(x, x, x, "scatter", 32)
+    with pytest.raises(ValueError, match="expected"):
+        intra_image_attn(x, x, x, "scatter", 64)
+    xr = x.clone().requires_grad_(True)
+    with pytest.raises(RuntimeError, match="forward-only"):
+        intra_llm_attn(xr, x, x)
+
+
+def test_non_default_stream_and_scale(lib):
+    q, k, v = oracle.make_inputs(2, 1536, 4, 4, seed=21, device="cuda")
+    st = torch.cuda.Stream()
+    from intra_b200 import intra_llm_attn
+    with torch.no_grad(), torch.cuda.stream(st):
+        out = intra_llm_attn(q, k, v, "gather1", group_num=8, softmax_scale=0.05)
+    st.synchronize()
+    ref = _util.oracle_attention(q, k, v, oracle.llm_gather1_mask(1536, 8), scale=0.05, on_device=True)
+    assert _util.max_abs_err(out, ref) <= _util.ATOL
