@@ -1,0 +1,397 @@
+"""Benchmark of the INTRA forward sparse-attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c5|c3]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+One step = one pass of the hot path over one batch of seeded synthetic q/k/v: for the default
+workload (B=1, S=16384, 32 query / 8 KV heads, head dim 128, bf16 N(0,1)) that is one Gather-1 G=8
+call and one window-576 call. Rank 0 prints ONE JSON line:
+
+  value       effective sparse TFLOP/s = 4*128*H*attended_pairs per step / device time per step,
+              summed over all ranks (each rank runs its own batch: weak scaling), inputs resident in
+              HBM, CUDA events on the launching stream, max over ranks
+  e2e         the same metric through the public Python API with pinned HOST buffers: per step the
+              q/k/v host->device copies, both calls, and the device->host copy of both outputs
+  roofline    tensor-core roofline of the dominant launch (the Gather-1 call): algorithmic FLOPs per
+              launch / its mean CUDA-event duration inside the timed region, against the measured
+              bf16 dense peak of MEASURED_PEAKS.json
+  cpu_baseline  the CPU oracle (fp32 dense-mask SDPA, the reference's reference.py algorithm) timed on
+              this box's host cores on a bounded sample of the same workload (rank 0, N=1 only)
+
+`--impl reference` times that CPU path alone (all host threads, bounded sample per step).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HEAD_DIM = 128
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+# dram__bytes_read.sum + dram__bytes_write.sum of one Gather-1 launch of the default workload, from
+# the ncu capture summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES = {"c2": None}
+
+WORKLOADS = {
+    # name: (description, B, S, H, Hkv, [(family, pattern, kwargs)])
+    "c1": ("LLM Scatter G=8 causal, B=1 S=4096 32q/8kv d=128", 1, 4096, 32, 8,
+           [("llm", "scatter", {"group_num": 8})]),
+    "c2": ("LLM Gather-1 G=8 + window 576 causal, B=1 S=16384 32q/8kv d=128", 1, 16384, 32, 8,
+           [("llm", "gather1", {"group_num": 8}), ("llm", "window", {"window": 576})]),
+    "c3": ("FLUX image Scatter + Gather-0, B=1 24 heads d=128, 512 text + 128x128 grid", 1, 512 + 128 * 128, 24, 24,
+           [("image", "scatter", {"width": 128}), ("image", "gather0", {"width": 128})]),
+    "c3s": ("FLUX image Scatter + Gather-0, B=1 24 heads d=128, 512 text + 64x64 grid", 1, 512 + 64 * 64, 24, 24,
+            [("image", "scatter", {"width": 64}), ("image", "gather0", {"width": 64})]),
+    "c4": ("g2s4 layer pair: Scatter G=2 + window 576 causal, B=1 S=32768 32q/8kv d=128", 1, 32768, 32, 8,
+           [("llm", "scatter", {"group_num": 2}), ("llm", "window", {"window": 576})]),
+    "c5": ("LLM Scatter G=8 + window 576 causal, B=1 S=65536 32q/8kv d=128", 1, 65536, 32, 8,
+           [("llm", "scatter", {"group_num": 8}), ("llm", "window", {"window": 576})]),
+}
+
+
+def pair_count(family, pattern, S, group_num=8, window=576, width=64):
+    """Attended (query, key) pairs of a pattern in closed form (popcount of its mask)."""
+    if family == "llm":
+        if pattern in ("scatter", "gather1"):
+            total = 0
+            for g in range(group_num):
+                if pattern == "scatter":
+                    n = S // group_num + (1 if g < S % group_num else 0)
+                else:
+                    span = group_num * group_num
+                    n = (S // span) * group_num + min(max(S % span - g * group_num, 0), group_num)
+                total += n * (n + 1) // 2
+            return total
+        total = 0
+        for b in range((S + 63) // 64):
+            first = max(64 * b - (window - 64), 0)
+            n = min(64 * b + 64, S) - 64 * b
+            total += n * (64 * b - first) + n * (n + 1) // 2
+        return total
+    n_img = width * width // 8
+    if pattern == "scatter":
+        return S * (512 + n_img)
+    return 512 * (512 + n_img) + width * width * (512 + 256)
+
+
+def call_flops(family, pattern, kw, S, H):
+    return 4 * HEAD_DIM * H * pair_count(family, pattern, S, **kw)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while a timed region runs (read-only)."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        except Exception:
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n = self._nvml
+        sm = n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(self._handle, n.NVML_CLOCK_SM)
+        r = n.nvmlDeviceGetCurrentClocksEventReasons(self._handle) if hasattr(
+            n, "nvmlDeviceGetCurrentClocksEventReasons") else n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+        reasons = []
+        if r & 0x8:
+            reasons.append("hw_slowdown")
+        if r & 0x40:
+            reasons.append("hw_thermal_slowdown")
+        if r & 0x20:
+            reasons.append("sw_thermal_slowdown")
+        if r & 0x4:
+            reasons.append("sw_power_cap")
+        return sm, mx, reasons
+
+    def _sample_smi(self):
+        out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                              "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+        f = [x.strip() for x in out.strip().split(",")]
+        reasons = [n for n, v in zip(self.NAMES, f[2:]) if v.lower().startswith("active")]
+        return float(f[0]), float(f[1]), reasons
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self._sample_nvml() if self._nvml else self._sample_smi())
+            except Exception:
+                pass
+            self._stop.wait(0.02 if self._nvml else 0.2)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=5)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        reasons = sorted({r for s in self.samples for r in s[2]})
+        return {"sm_mhz": statistics.median(s[0] for s in self.samples),
+                "sm_max_mhz": max(s[1] for s in self.samples), "reasons": reasons, "samples": len(self.samples)}
+
+
+class CpuSample:
+    """A bounded sample of the workload for the CPU oracle: every `stride`-th query row of the first
+    KV-head group (H/Hkv query heads, 1 KV head) of every call of the step, against all keys. The
+    attended pairs of exactly those rows are counted from the mask, so the throughput is in the same
+    effective-sparse-FLOP unit as the GPU's."""
+
+    def __init__(self, workload, threads, stride=1):
+        import torch
+
+        from oracle import intra_oracle as oracle
+        self.oracle = oracle
+        desc, B, S, H, Hkv, calls = WORKLOADS[workload]
+        self.rep = H // Hkv
+        torch.set_num_threads(threads)
+        self.q, self.k, self.v = oracle.make_inputs(1, S, self.rep, 1, seed=0)
+        self.masks = [torch.from_numpy(oracle.build_mask(f, p, S, **kw)) for f, p, kw in calls]
+        self.S, self.Hkv = S, Hkv
+        self.set_stride(stride)
+
+    def set_stride(self, stride):
+        self.stride = stride
+        self.qs = self.q[:, ::stride].contiguous()
+        self.ms = [m[::stride].contiguous() for m in self.masks]
+        self.flops = sum(4 * HEAD_DIM * self.rep * int(m.sum()) for m in self.ms)
+
+    def run(self):
+        t0 = time.perf_counter()
+        for m in self.ms:
+            self.oracle.masked_attention(self.qs, self.k, self.v, m)
+        return time.perf_counter() - t0
+
+    def describe(self):
+        rows = "all query rows" if self.stride == 1 else f"every {self.stride}th query row"
+        return (f"{rows} of {self.rep} query heads / 1 KV head (one KV-head group of {self.Hkv}) "
+                f"of each call, all keys, B=1, S={self.S}")
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path (its fp32 dense-mask SDPA oracle, restated in
+    oracle/) on the host cores; each step is a bounded sample of the workload, thinned so that the
+    whole run stays within a couple of minutes."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    threads = os.cpu_count() or 1
+    desc = WORKLOADS[args.workload][0]
+    sample = CpuSample(args.workload, threads, stride=16)
+    sample.run()
+    per_row = sample.run() / (sample.S // 16)                 # seconds per sampled query row
+    budget = 100.0 / max(args.steps + args.warmup, 1)          # seconds per step
+    stride = 1
+    while stride < 64 and per_row * (sample.S // stride) > budget:
+        stride *= 2
+    sample.set_stride(stride)
+    for _ in range(args.warmup):
+        sample.run()
+    total = sum(sample.run() for _ in range(args.steps))
+    value = sample.flops * args.steps / total / 1e12
+    line = {
+        "impl": "reference", "metric": "effective sparse attention throughput (4*d*H*attended pairs / time)",
+        "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "inputs": "seeded bf16 N(0,1), computed in fp32 on the CPU"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": sample.describe()},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from intra_b200 import intra_image_attn, intra_llm_attn
+    from intra_b200.interface import device_status
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: the attention path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    desc, B, S, H, Hkv, calls = WORKLOADS[args.workload]
+    g = torch.Generator(device="cpu").manual_seed(1000 + rank)
+    hq = torch.randn(B, S, H, HEAD_DIM, generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
+    hk = torch.randn(B, S, Hkv, HEAD_DIM, generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
+    hv = torch.randn(B, S, Hkv, HEAD_DIM, generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
+    q, k, v = hq.to(dev), hk.to(dev), hv.to(dev)
+    houts = [torch.empty_like(hq).pin_memory() for _ in calls]
+
+    def run_call(c, q_, k_, v_):
+        family, pattern, kw = c
+        if family == "llm":
+            return intra_llm_attn(q_, k_, v_, pattern, **kw)
+        return intra_image_attn(q_, k_, v_, pattern, **kw)
+
+    flops_calls = [call_flops(f, p, kw, S, H) for f, p, kw in calls]
+    flops_step = sum(flops_calls)
+    dom = max(range(len(calls)), key=lambda i: flops_calls[i])       # dominant launch
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            for c in calls:
+                run_call(c, q, k, v)
+        torch.cuda.synchronize()
+
+        # ---- device-resident timed region: K steps, events around the region and around each launch
+        evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in calls]
+               for _ in range(args.steps)]
+        t_beg, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with ClockSampler(local_rank) as clocks:
+            t_beg.record(stream)
+            for s in range(args.steps):
+                for i, c in enumerate(calls):
+                    evs[s][i][0].record(stream)
+                    run_call(c, q, k, v)
+                    evs[s][i][1].record(stream)
+            t_end.record(stream)
+            barrier()
+        total_ms = t_beg.elapsed_time(t_end)
+        launch_ms = [statistics.mean(evs[s][i][0].elapsed_time(evs[s][i][1]) for s in range(args.steps))
+                     for i in range(len(calls))]
+
+        # ---- end-to-end: pinned host buffers in, host buffers out, every step
+        e_steps = max(3, min(args.steps, 20))
+        for _ in range(2):
+            dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
+            for i, c in enumerate(calls):
+                houts[i].copy_(run_call(c, dq, dk, dv), non_blocking=True)
+        e_beg, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e_beg.record(stream)
+        for _ in range(e_steps):
+            dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
+            for i, c in enumerate(calls):
+                houts[i].copy_(run_call(c, dq, dk, dv), non_blocking=True)
+        e_end.record(stream)
+        barrier()
+        e2e_ms = e_beg.elapsed_time(e_end)
+
+    status = device_status(local_rank, reset=True)
+    if status != 0:
+        raise SystemExit(f"kernel status word {status}: a bounded wait gave up; numbers invalid")
+
+    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = times.tolist()
+    if rank == 0:
+        peaks, peaks_kind = load_peaks()
+        ms_per_step = total_ms / args.steps
+        value = world * flops_step / (ms_per_step * 1e-3) / 1e12
+        e2e_value = world * flops_step / (e2e_ms / e_steps * 1e-3) / 1e12
+        achieved = flops_calls[dom] / (launch_ms[dom] * 1e-3) / 1e12
+        peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        line = {
+            "metric": "effective sparse attention throughput (4*d*H*attended pairs / time)",
+            "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": desc, "per_rank": "each rank runs the whole workload on its own seeded batch",
+                       "l2": "inputs+outputs per step (%d MB) exceed the 126 MB L2; no explicit flush" % (
+                           (2 * q.numel() + k.numel() + v.numel()) * 2 // 2**20),
+                       "calls": [{"pattern": f"{f}/{p}", **kw, "ms": launch_ms[i], "tflops": flops_calls[i] / launch_ms[i] / 1e9}
+                                 for i, (f, p, kw) in enumerate(calls)]},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": (hq.numel() + hk.numel() + hv.numel()) * 2,
+                    "d2h_bytes_per_step": sum(h.numel() for h in houts) * 2, "steps": e_steps,
+                    "ms_per_step": e2e_ms / e_steps},
+            "gpu_launches": args.steps * len(calls),
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "tensor", "kernel": "intra_fwd_kernel (%s/%s launch)" % (calls[dom][0], calls[dom][1]),
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_source": peaks_kind + " bf16_tflops (burst)",
+                         "frac_of_sustained": achieved / float(peaks.get("bf16_tflops_sustained", peak)),
+                         "flops_per_launch": flops_calls[dom], "ms_per_launch": launch_ms[dom],
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
+        }
+        if world == 1 and not args.no_cpu:
+            threads = os.cpu_count() or 1
+            sample = CpuSample(args.workload, threads, stride=1)
+            sample.run()                                                # warm-up
+            dts = [sample.run() for _ in range(3)]
+            line["cpu_baseline"] = {"value": sample.flops / statistics.median(dts) / 1e12, "unit": "TFLOP/s",
+                                    "cores": threads, "kind": "port",
+                                    "sample": sample.describe() + "; median of 3 after 1 warm-up"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "ours" and args.gpus != world:
+        if args.gpus > 1 and world == 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus))
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
