@@ -89,6 +89,36 @@ int intra_b200_tile_counts(int family, int pattern, int S, int param, int64_t* n
 int intra_b200_selftest_umma(const void* a, const void* b, const void* v, float p_scale,
                              float* s_out, float* o_out, int device, void* cuda_stream);
 
+/* intra_b200_fwd_llm for hosts that cannot let a library allocate device memory. It has no
+ * counterpart in the reference.
+ *
+ * Who needs it: a serving engine or trainer that reserves (nearly) all of HBM for its own arena at
+ * start-up leaves nothing for a cudaMalloc made later from inside a library, and a latency-bound
+ * serving thread cannot afford the device-wide synchronisation a cudaMalloc implies. The regular
+ * entry points allocate once per device (a status word the kernel reports to); this one never calls
+ * cudaMalloc, cudaFree or any other allocating routine. The caller still passes q, k, v and out.
+ *
+ * The kernel's scratch - today that one status word - lives in a fixed 256-byte array that is part of
+ * the library image, so every GPU that loads the library carries those 256 bytes until the process
+ * exits. A launch whose scratch would not fit in the array is refused with INTRA_ERR_UNSUPPORTED;
+ * with the present kernel the scratch does not grow with the problem, so no attention shape is
+ * refused for that reason. All other argument rules and status codes are those of
+ * intra_b200_fwd_llm.
+ *
+ * The first call on a device looks up the array's device address (with that device made current)
+ * and opts the kernel into its shared-memory size; make that first call before any stream capture.
+ * Every call on a device shares the array: the call clears the status word on `cuda_stream` before
+ * its launch, so calls whose GPU work overlaps (different streams, or threads racing on one device)
+ * race on that word - serialise them on one stream. The array keeps what the last call left: pass a
+ * non-null `prev_status` to have the call first synchronise `cuda_stream` and copy out the word left
+ * by the previous call (0 = healthy, also before the first call); pass NULL to stay asynchronous. */
+int intra_b200_fwd_llm_noalloc(const void* q, const void* k, const void* v, void* out,
+                               int B, int S, int H, int Hkv,
+                               const int64_t q_strides[3], const int64_t k_strides[3],
+                               const int64_t v_strides[3], const int64_t out_strides[3],
+                               int pattern, int group_num, int window, float softmax_scale,
+                               int device, void* cuda_stream, int* prev_status);
+
 #ifdef __cplusplus
 }
 #endif

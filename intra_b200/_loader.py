@@ -23,6 +23,8 @@ SIGNATURES = {
                                 _i, _i, _i, _f, _i, _vp]),
     "intra_b200_fwd_image": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _I64x3, _I64x3, _I64x3, _I64x3,
                                   _i, _i, _f, _i, _vp]),
+    "intra_b200_fwd_llm_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _I64x3, _I64x3, _I64x3, _I64x3,
+                                        _i, _i, _i, _f, _i, _vp, ctypes.POINTER(_i)]),
     "intra_b200_strerror": (ctypes.c_char_p, [_i]),
     "intra_b200_last_cuda_error": (_i, []),
     "intra_b200_device_status": (_i, [_i, ctypes.POINTER(_i), _i]),
@@ -38,7 +40,10 @@ def _load():
         raise ImportError(f"{LIB_PATH} is not built; run `python -m intra_b200.build` (needs nvcc)")
     lib = ctypes.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():
-        fn = getattr(lib, name)
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as err:  # library older than this file
+            raise ImportError(f"{LIB_PATH} lacks {name}; rebuild with `python -m intra_b200.build --force`") from err
         fn.restype, fn.argtypes = res, args
     return lib
 

@@ -95,6 +95,41 @@ int problem_from(int family, int pattern, int S, int param, Problem* prob) {
   return INTRA_OK;
 }
 
+// ---- scratch for intra_b200_fwd_llm_noalloc -------------------------------------------------------
+// The attention kernel's only scratch is the status word it reports to. For callers that must not
+// allocate, that word lives in this fixed array, which every GPU that loads the library holds until
+// the process exits. Host code sees only a stand-in for the array under this name; its device
+// address is fetched once per device with cudaGetSymbolAddress and handed to the kernel.
+constexpr size_t NOALLOC_SCRATCH_BYTES = 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+struct NoAllocState {
+  std::once_flag once;
+  int init_status = INTRA_OK;
+  int* scratch = nullptr;         // device address of g_noalloc_scratch on this device
+};
+NoAllocState g_noalloc[MAX_DEVICES];
+
+// Runs once per device with that device current. Allocates nothing.
+void init_noalloc(int device) {
+  NoAllocState& st = g_noalloc[device];
+  int major = 0;
+  cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+  if (e != cudaSuccess) { st.init_status = cuda_fail(e); return; }
+  if (major != 10) { st.init_status = INTRA_ERR_DEVICE; return; }
+  e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+  void* ptr = nullptr;
+  if (e == cudaSuccess) e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+  if (e != cudaSuccess) { st.init_status = cuda_fail(e); return; }
+  st.scratch = static_cast<int*>(ptr);
+}
+
+// Bytes of scratch one launch of the attention kernel needs: its status word.
+size_t fwd_scratch_bytes(const Problem&) { return sizeof(int); }
+
 int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, int S, int H, int Hkv,
                const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, int family, int pattern,
                int param, float softmax_scale, int device, void* stream) {
@@ -249,6 +284,57 @@ int intra_b200_selftest_umma(const void* a, const void* b, const void* v, float 
       static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
       static_cast<const __nv_bfloat16*>(v), p_scale, s_out, o_out, g_dev[device].status_word);
   cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
+}
+
+int intra_b200_fwd_llm_noalloc(const void* q, const void* k, const void* v, void* out, int B, int S, int H, int Hkv,
+                               const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                               const int64_t out_strides[3], int pattern, int group_num, int window,
+                               float softmax_scale, int device, void* cuda_stream, int* prev_status) {
+  if (!q || !k || !v || !out || B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0) return INTRA_ERR_BAD_ARG;
+  if (!q_strides || !k_strides || !v_strides || !out_strides) return INTRA_ERR_BAD_ARG;
+  if (!(softmax_scale > 0.f) || !std::isfinite(softmax_scale)) return INTRA_ERR_BAD_ARG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !strides_ok(q_strides) ||
+      !strides_ok(k_strides) || !strides_ok(v_strides) || !strides_ok(out_strides))
+    return INTRA_ERR_ALIGNMENT;
+  if (device < 0 || device >= MAX_DEVICES) return INTRA_ERR_BAD_ARG;
+  FwdParams p;
+  int rc = problem_from(0, pattern, S, pattern == INTRA_LLM_WINDOW ? window : group_num, &p.prob);
+  if (rc != INTRA_OK) return rc;
+  const int64_t blocks = int64_t(p.prob.n_tiles) * B * H;
+  if (blocks <= 0 || blocks > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
+  // The launch's scratch has to fit the fixed array; a shape that needed more is turned away here.
+  if (fwd_scratch_bytes(p.prob) > NOALLOC_SCRATCH_BYTES) return INTRA_ERR_UNSUPPORTED;
+
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  NoAllocState& st = g_noalloc[device];
+  std::call_once(st.once, init_noalloc, device);
+  if (st.init_status != INTRA_OK) return st.init_status;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e;
+  if (prev_status) {      // what the previous call on this device left behind (0 before the first call)
+    e = cudaStreamSynchronize(stream);
+    if (e == cudaSuccess) e = cudaMemcpy(prev_status, st.scratch, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  e = cudaMemsetAsync(st.scratch, 0, sizeof(int), stream);   // the status word must start at zero
+  if (e != cudaSuccess) return cuda_fail(e);
+
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k = static_cast<const __nv_bfloat16*>(k);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.o = static_cast<__nv_bfloat16*>(out);
+  p.qs = {q_strides[0], q_strides[1], q_strides[2]};
+  p.ks = {k_strides[0], k_strides[1], k_strides[2]};
+  p.vs = {v_strides[0], v_strides[1], v_strides[2]};
+  p.os = {out_strides[0], out_strides[1], out_strides[2]};
+  p.B = B; p.H = H; p.Hkv = Hkv;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = st.scratch;
+  intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, stream>>>(p);
+  e = cudaGetLastError();
   return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
 }
 
