@@ -78,6 +78,10 @@ int intra_b200_device_status(int device, int* status_word, int reset);
 int intra_b200_visited_host(int family, int pattern, int S, int param, uint8_t* counts);
 int intra_b200_visited_device(int family, int pattern, int S, int param, uint8_t* counts_dev,
                               int device, void* cuda_stream);
+/* Same as intra_b200_visited_host for the decomposition into pairs of row tiles that share their
+ * key tiles (used when the query heads of a KV group cannot be paired); INTRA_ERR_UNSUPPORTED for
+ * Gather-0, which has no such pairs. */
+int intra_b200_visited_pairs_host(int family, int pattern, int S, int param, uint8_t* counts);
 
 /* Test hook: number of tiles (CTAs per batch and head) and key tiles summed over them, i.e. the
  * tensor-core work the launch does in units of 128 x 128 score tiles. */

@@ -29,6 +29,7 @@ SIGNATURES = {
     "intra_b200_last_cuda_error": (_i, []),
     "intra_b200_device_status": (_i, [_i, ctypes.POINTER(_i), _i]),
     "intra_b200_visited_host": (_i, [_i, _i, _i, _i, _vp]),
+    "intra_b200_visited_pairs_host": (_i, [_i, _i, _i, _i, _vp]),
     "intra_b200_visited_device": (_i, [_i, _i, _i, _i, _vp, _i, _vp]),
     "intra_b200_tile_counts": (_i, [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]),
     "intra_b200_selftest_umma": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _i, _vp]),

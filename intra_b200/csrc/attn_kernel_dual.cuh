@@ -1,0 +1,417 @@
+// Persistent, ping-pong forward kernel: each CTA owns one SM and walks a static list of pair tiles
+// (intra_index.h): two 128-row query sub-tiles that share every K / V tile brought into shared
+// memory. While one sub-tile's softmax runs on the CUDA cores, the tensor core works on the
+// other's QK^T and PV, so the two pipes overlap inside one CTA:
+//
+//   warps 0-3    softmax / correction / epilogue of sub-tile 0   (TMEM: S0 cols 0-127,   O0 cols 256-383)
+//   warps 4-7    the same for sub-tile 1                         (TMEM: S1 cols 128-255, O1 cols 384-511)
+//   warps 8-11   loaders: index maps + cp.async row gathers of Q0, Q1 and a 2-stage ring each for K, V;
+//                completion is signalled by the copies themselves (cp.async.mbarrier.arrive), so the
+//                loaders never wait for data, only for free slots
+//   warp 12      one thread issues tcgen05.mma in the order QK0(n) PV1(n-1) QK1(n) PV0(n), carried on
+//                across tile boundaries so the next tile's first QK^T overlaps this tile's last softmax
+//
+// Items are dealt to CTAs heaviest first in boustrophedon order, which needs no counters in global
+// memory. Every wait is bounded; see attn_kernel.cuh for the abort protocol, which is the same.
+//
+// Replaces, like attn_kernel.cuh, the reference's compute_attn_1rowblock_* kernels
+// (csrc/flash_attn/src/flash_fwd_kernel.h:3970-6158) for every pattern whose tiles pair up.
+#pragma once
+#include "attn_kernel.cuh"
+
+namespace intra {
+
+constexpr int DUAL_THREADS = 512;
+constexpr int KV_STAGES = 2;
+constexpr int DUAL_SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + 1024;   // Q0 Q1 | K ring | V ring
+constexpr int DUAL_TMEM_COLS = 512;
+
+struct DualParams {
+  FwdParams f;
+  int row_pairs;        // 0: sub-tiles are two heads of one KV group; 1: two row tiles of one head
+  int n_pair_tiles;     // pair tiles per (batch, head or head pair)
+  int heads_per_item;   // row_pairs ? H : H / 2  (number of items per pair tile and batch)
+  int n_items;          // n_pair_tiles * B * heads_per_item
+};
+
+struct DualItem {
+  PairTile pt;
+  int b, h0, h1, hk;
+};
+
+// Item number `seq` of this CTA: heaviest-first list dealt round by round, every other round reversed.
+__device__ __forceinline__ int dual_item_index(int seq, int cta, int n_cta) {
+  return seq * n_cta + ((seq & 1) ? (n_cta - 1 - cta) : cta);
+}
+
+__device__ __forceinline__ DualItem dual_decode(const DualParams& p, int item) {
+  DualItem it;
+  const int per_tile = p.f.B * p.heads_per_item;
+  const int idx = item / per_tile;
+  const int rem = item % per_tile;
+  it.b = rem / p.heads_per_item;
+  const int hh = rem % p.heads_per_item;
+  if (p.row_pairs) { it.h0 = it.h1 = hh; } else { it.h0 = 2 * hh; it.h1 = 2 * hh + 1; }
+  it.hk = it.h0 / (p.f.H / p.f.Hkv);
+  it.pt = make_pair(p.f.prob, p.row_pairs, idx);
+  return it;
+}
+
+__global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const DualParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // barriers: 0 q_full, 1 q_empty, 2-3 k_full, 4-5 k_empty, 6-7 v_full, 8-9 v_empty,
+  //           10-11 s_full[s], 12-13 p_full[s], 14-15 o_done[s], 16 drain
+  __shared__ uint64_t bars[17];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (tid == 0) abort_flag = *reinterpret_cast<volatile int*>(p.f.status);
+  __syncthreads();
+  if (abort_flag != 0) return;                          // an earlier launch or CTA already failed
+  __syncthreads();
+
+  uint64_t* q_full = &bars[0];
+  uint64_t* q_empty = &bars[1];
+  uint64_t* k_full = &bars[2];
+  uint64_t* k_empty = &bars[4];
+  uint64_t* v_full = &bars[6];
+  uint64_t* v_empty = &bars[8];
+  uint64_t* s_full = &bars[10];
+  uint64_t* p_full = &bars[12];
+  uint64_t* o_done = &bars[14];
+  uint64_t* drain = &bars[16];
+
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem0 = smem_base;                                 // Q sub-tile s at + s * TILE_BYTES
+  const uint32_t k_smem0 = smem_base + 2 * TILE_BYTES;                // K stage j at + j * TILE_BYTES
+  const uint32_t v_smem0 = smem_base + (2 + KV_STAGES) * TILE_BYTES;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    ptx::mbar_init(q_full, 128);
+    ptx::mbar_init(q_empty, 1);
+    for (int j = 0; j < KV_STAGES; ++j) {
+      ptx::mbar_init(&k_full[j], 128);
+      ptx::mbar_init(&k_empty[j], 1);
+      ptx::mbar_init(&v_full[j], 128);
+      ptx::mbar_init(&v_empty[j], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(&s_full[s], 1);
+      ptx::mbar_init(&p_full[s], 128);
+      ptx::mbar_init(&o_done[s], 1);
+    }
+    ptx::mbar_init(drain, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0) {
+    ptx::tmem_alloc(&tmem_base_smem, DUAL_TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = tmem_base_smem;
+  volatile int* abort_p = &abort_flag;
+  const int n_cta = gridDim.x;
+  const int cta = blockIdx.x;
+
+  if (warp < 8) {
+    // ================================ softmax / correction / epilogue ==========================
+    ptx::setmaxnreg_inc<192>();
+    const int s_idx = warp >> 2;                          // which sub-tile
+    const int row = tid & 127;                            // TMEM lane == query row of the sub-tile
+    const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
+    const uint32_t s_addr = lane_addr + s_idx * 128;
+    const uint32_t o_addr = lane_addr + 256 + s_idx * 128;
+    uint64_t* my_s_full = &s_full[s_idx];
+    uint64_t* my_p_full = &p_full[s_idx];
+    uint64_t* my_o_done = &o_done[s_idx];
+    const float scale_log2 = p.f.scale_log2;
+    uint32_t it = 0;                                      // key tiles processed so far (barrier phases)
+    bool ok = true;
+
+    for (int seq = 0; ok; ++seq) {
+      const int item = dual_item_index(seq, cta, n_cta);
+      if (item >= p.n_items) break;
+      const DualItem di = dual_decode(p, item);
+      const int n_kv = di.pt.kv.n_kv_tiles;
+      if (n_kv == 0) continue;
+      int token, lo, hi;
+      pair_q_row(p.f.prob, di.pt, s_idx, row, &token, &lo, &hi);
+      float m_run = -CUDART_INF_F;
+      float l_run = 0.f;
+
+      for (int n = 0; n < n_kv; ++n, ++it) {
+        ok = ptx::mbar_wait(my_s_full, it & 1, abort_p);
+        if (!ok) { if (*abort_p == 1) *abort_p = 11 + s_idx; break; }
+        ptx::tc_fence_after();
+
+        float s[TILE_N];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_addr + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
+        ptx::tmem_wait_ld();
+
+        const int u0 = n * TILE_N;
+        if (lo > u0 || hi < u0 + TILE_N - 1) {            // this row's interval does not cover the tile
+#pragma unroll
+          for (int c = 0; c < TILE_N; ++c) {
+            const int u = u0 + c;
+            if (u < lo || u > hi) s[c] = -CUDART_INF_F;
+          }
+        }
+        float tmax = s[0];
+#pragma unroll
+        for (int c = 1; c < TILE_N; ++c) tmax = fmaxf(tmax, s[c]);
+        const float m_new = fmaxf(m_run, tmax);
+        const bool grow = (m_new - m_run) * scale_log2 > RESCALE_THRESHOLD;
+        float alpha = 1.f;
+        if (grow) {
+          alpha = ptx::ex2((m_run - m_new) * scale_log2);
+          l_run *= alpha;
+          m_run = m_new;
+        }
+        if (n > 0 && __any_sync(0xffffffffu, grow)) {     // rare once the maximum has settled
+          ok = ptx::mbar_wait(my_o_done, (it - 1) & 1, abort_p);   // PV of the previous key tile has landed
+          if (!ok) { if (*abort_p == 1) *abort_p = 13 + s_idx; break; }
+          ptx::tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < HEAD_DIM / 16; ++c) {
+            uint32_t o[16];
+            ptx::tmem_ld16(o_addr + c * 16, o);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            ptx::tmem_st16(o_addr + c * 16, o);
+          }
+        }
+        const float base = (m_run == -CUDART_INF_F) ? 0.f : m_run * scale_log2;
+        float lsum = 0.f;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {                  // 32 scores -> 16 packed columns of P
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float p0 = ptx::ex2(fmaf(s[c4 * 32 + 2 * c], scale_log2, -base));
+            const float p1 = ptx::ex2(fmaf(s[c4 * 32 + 2 * c + 1], scale_log2, -base));
+            lsum += p0 + p1;
+            pk[c] = ptx::pack_bf16(p0, p1);
+          }
+          ptx::tmem_st16(s_addr + c4 * 16, pk);
+        }
+        l_run += lsum;
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(my_p_full);
+      }
+      if (!ok) break;
+
+      ok = ptx::mbar_wait(my_o_done, (it - 1) & 1, abort_p);       // last PV of this item
+      if (!ok) { if (*abort_p == 1) *abort_p = 15 + s_idx; break; }
+      ptx::tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const int h = s_idx ? di.h1 : di.h0;
+      __nv_bfloat16* dst = p.f.o + di.b * p.f.os.sb + int64_t(token < 0 ? 0 : token) * p.f.os.ss + h * p.f.os.sh;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        ptx::tmem_ld32(o_addr + c * 32, o);
+        ptx::tmem_wait_ld();
+        if (token >= 0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = ptx::pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+            w.y = ptx::pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+            w.z = ptx::pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+            w.w = ptx::pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = w;
+          }
+        }
+      }
+      // The next item's first PV overwrites O only after this warp's next p_full arrive, which is
+      // ordered after these loads; S is rewritten by the tensor core only after the last PV above.
+      ptx::tc_fence_before();
+    }
+  } else if (warp < 12) {
+    // ================================ loaders ===================================================
+    ptx::setmaxnreg_dec<64>();
+    const int lt = tid - 256;
+    const int chunk = lt & 15;                            // 16-byte chunk of the 256-byte row
+    const int rsub = lt >> 4;                             // row within a pass of 8 rows
+    uint32_t kc = 0;                                      // K / V tiles loaded so far (ring position)
+    bool ok = true;
+    int n_done = 0;
+
+    for (int seq = 0; ok; ++seq) {
+      const int item = dual_item_index(seq, cta, n_cta);
+      if (item >= p.n_items) break;
+      const DualItem di = dual_decode(p, item);
+      const int n_kv = di.pt.kv.n_kv_tiles;
+      if (n_kv == 0) continue;
+      if (n_done > 0) {                                   // Q buffers free once the previous item's last QK^T is done
+        ok = ptx::mbar_wait(q_empty, (n_done - 1) & 1, abort_p);
+        if (!ok) { if (*abort_p == 1) *abort_p = 21; break; }
+      }
+      {
+        const __nv_bfloat16* qb0 = p.f.q + di.b * p.f.qs.sb + di.h0 * p.f.qs.sh + chunk * 8;
+        const __nv_bfloat16* qb1 = p.f.q + di.b * p.f.qs.sb + di.h1 * p.f.qs.sh + chunk * 8;
+#pragma unroll 4
+        for (int ps = 0; ps < TILE_M / 8; ++ps) {
+          const int row = ps * 8 + rsub;
+          int token, lo, hi;
+          pair_q_row(p.f.prob, di.pt, 0, row, &token, &lo, &hi);
+          const void* src = token >= 0 ? static_cast<const void*>(qb0 + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
+          ptx::cp_async_16(q_smem0 + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+          if (p.row_pairs) pair_q_row(p.f.prob, di.pt, 1, row, &token, &lo, &hi);
+          src = token >= 0 ? static_cast<const void*>(qb1 + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
+          ptx::cp_async_16(q_smem0 + TILE_BYTES + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+        }
+        ptx::cp_async_mbar_arrive_noinc(q_full);
+      }
+      const __nv_bfloat16* kb = p.f.k + di.b * p.f.ks.sb + di.hk * p.f.ks.sh + chunk * 8;
+      const __nv_bfloat16* vb = p.f.v + di.b * p.f.vs.sb + di.hk * p.f.vs.sh + chunk * 8;
+      for (int n = 0; n < n_kv && ok; ++n, ++kc) {
+        const int stage = kc % KV_STAGES;
+        const uint32_t use = kc / KV_STAGES;              // how often this stage has been filled before
+        int tokens[TILE_N / 8];
+#pragma unroll
+        for (int ps = 0; ps < TILE_N / 8; ++ps) tokens[ps] = key_token(p.f.prob, di.pt.kv, n * TILE_N + ps * 8 + rsub);
+        if (use > 0) {
+          ok = ptx::mbar_wait(&k_empty[stage], (use - 1) & 1, abort_p);
+          if (!ok) { if (*abort_p == 1) *abort_p = 22; break; }
+        }
+        const uint32_t kdst = k_smem0 + stage * TILE_BYTES;
+#pragma unroll
+        for (int ps = 0; ps < TILE_N / 8; ++ps) {
+          const int row = ps * 8 + rsub;
+          const int token = tokens[ps];
+          const void* src = token >= 0 ? static_cast<const void*>(kb + int64_t(token) * p.f.ks.ss) : static_cast<const void*>(p.f.k);
+          ptx::cp_async_16(kdst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+        }
+        ptx::cp_async_mbar_arrive_noinc(&k_full[stage]);
+        if (use > 0) {
+          ok = ptx::mbar_wait(&v_empty[stage], (use - 1) & 1, abort_p);
+          if (!ok) { if (*abort_p == 1) *abort_p = 23; break; }
+        }
+        const uint32_t vdst = v_smem0 + stage * TILE_BYTES;
+#pragma unroll
+        for (int ps = 0; ps < TILE_N / 8; ++ps) {
+          const int row = ps * 8 + rsub;
+          const int token = tokens[ps];
+          const void* src = token >= 0 ? static_cast<const void*>(vb + int64_t(token) * p.f.vs.ss) : static_cast<const void*>(p.f.v);
+          ptx::cp_async_16(vdst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+        }
+        ptx::cp_async_mbar_arrive_noinc(&v_full[stage]);
+      }
+      ++n_done;
+    }
+    ptx::cp_async_commit();
+    ptx::cp_async_wait<0>();
+  } else {
+    // ================================ MMA issue ==================================================
+    ptx::setmaxnreg_dec<64>();
+    if (warp == 12) {
+      uint32_t kc = 0;                                    // key tiles issued so far
+      uint32_t it0 = 0, it1 = 0;                          // PVs issued per sub-tile (p_full phases)
+      bool pend = false;                                  // PV1 of the previous key tile not yet issued
+      uint32_t pend_acc = 0, pend_stage = 0;
+      int n_done = 0;
+      bool ok = true;
+
+      for (int seq = 0; ok; ++seq) {
+        const int item = dual_item_index(seq, cta, n_cta);
+        if (item >= p.n_items) break;
+        const DualItem di = dual_decode(p, item);
+        const int n_kv = di.pt.kv.n_kv_tiles;
+        if (n_kv == 0) continue;
+        ok = ptx::mbar_wait(q_full, n_done & 1, abort_p);
+        if (!ok) { if (*abort_p == 1) *abort_p = 31; break; }
+        for (int n = 0; n < n_kv; ++n, ++kc) {
+          const int stage = kc % KV_STAGES;
+          const uint32_t par = (kc / KV_STAGES) & 1;
+          ok = ptx::mbar_wait(&k_full[stage], par, abort_p);
+          if (!ok) { if (*abort_p == 1) *abort_p = 32; break; }
+          ptx::fence_proxy_async_smem();
+          ptx::tc_fence_after();
+          const uint32_t k_smem = k_smem0 + stage * TILE_BYTES;
+          if (lane == 0) {
+            issue_qk(q_smem0, k_smem, tmem + 0);
+            ptx::mma_commit(&s_full[0]);
+          }
+          __syncwarp();
+          if (pend) {
+            ok = ptx::mbar_wait(&p_full[1], it1 & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 33; break; }
+            ptx::tc_fence_after();
+            if (lane == 0) {
+              issue_pv(tmem + 128, v_smem0 + pend_stage * TILE_BYTES, tmem + 384, pend_acc != 0);
+              ptx::mma_commit(&o_done[1]);
+              ptx::mma_commit(&v_empty[pend_stage]);
+            }
+            __syncwarp();
+            ++it1;
+            pend = false;
+          }
+          if (lane == 0) {
+            issue_qk(q_smem0 + TILE_BYTES, k_smem, tmem + 128);
+            ptx::mma_commit(&s_full[1]);
+            ptx::mma_commit(&k_empty[stage]);
+            if (n == n_kv - 1) ptx::mma_commit(q_empty);
+          }
+          __syncwarp();
+          ok = ptx::mbar_wait(&v_full[stage], par, abort_p);
+          if (!ok) { if (*abort_p == 1) *abort_p = 34; break; }
+          ptx::fence_proxy_async_smem();
+          ok = ptx::mbar_wait(&p_full[0], it0 & 1, abort_p);
+          if (!ok) { if (*abort_p == 1) *abort_p = 35; break; }
+          ptx::tc_fence_after();
+          if (lane == 0) {
+            issue_pv(tmem + 0, v_smem0 + stage * TILE_BYTES, tmem + 256, n > 0);
+            ptx::mma_commit(&o_done[0]);
+          }
+          __syncwarp();
+          ++it0;
+          pend = true;
+          pend_acc = n > 0 ? 1u : 0u;
+          pend_stage = stage;
+        }
+        ++n_done;
+      }
+      if (ok && pend) {
+        ok = ptx::mbar_wait(&p_full[1], it1 & 1, abort_p);
+        if (!ok && *abort_p == 1) *abort_p = 36;
+        if (ok) {
+          ptx::tc_fence_after();
+          if (lane == 0) {
+            issue_pv(tmem + 128, v_smem0 + pend_stage * TILE_BYTES, tmem + 384, pend_acc != 0);
+            ptx::mma_commit(&o_done[1]);
+            ptx::mma_commit(&v_empty[pend_stage]);
+          }
+          __syncwarp();
+        }
+      }
+      if (!ok) {                                          // let MMAs in flight finish before TMEM is freed
+        if (lane == 0) ptx::mma_commit(drain);
+        __syncwarp();
+        int dummy = 0;
+        ptx::mbar_wait(drain, 0, &dummy, 100);
+      }
+    }
+  }
+
+  // ---- teardown --------------------------------------------------------------------------------
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, DUAL_TMEM_COLS);
+  }
+  if (tid == 0 && abort_flag != 0) atomicCAS(p.f.status, 0, STATUS_WAIT_BASE + abort_flag);
+}
+
+}  // namespace intra

@@ -7,10 +7,12 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
 #include "attn_kernel.cuh"
+#include "attn_kernel_dual.cuh"
 #include "selftest.cuh"
 
 namespace {
@@ -24,6 +26,7 @@ struct DeviceState {
   std::once_flag once;
   int init_status = INTRA_OK;
   int* status_word = nullptr;     // device memory, one int
+  int sm_count = 0;
 };
 DeviceState g_dev[MAX_DEVICES];
 
@@ -59,6 +62,9 @@ void init_device(int device) {
                              cudaSharedmemCarveoutMaxShared);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+  st.sm_count = prop.multiProcessorCount;
   if (e == cudaSuccess) e = cudaMalloc(&st.status_word, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(st.status_word, 0, sizeof(int));
   if (e != cudaSuccess) st.init_status = cuda_fail(e);
@@ -161,7 +167,23 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
   p.B = B; p.H = H; p.Hkv = Hkv;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = g_dev[device].status_word;
-  intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  // Patterns whose tiles pair up run on the persistent two-sub-tile kernel; Gather-0, whose tiles share
+  // no keys, on the one-tile kernel (INTRA_B200_SINGLE_TILE=1 forces the latter everywhere, for A/B runs).
+  static const bool force_single = [] { const char* v = std::getenv("INTRA_B200_SINGLE_TILE"); return v && v[0] == '1'; }();
+  if (p.prob.kind != KIND_IMG_GATHER0 && !force_single) {
+    DualParams d;
+    d.f = p;
+    d.row_pairs = ((H / Hkv) % 2 == 0) ? 0 : 1;
+    d.n_pair_tiles = n_pair_tiles(p.prob, d.row_pairs);
+    d.heads_per_item = d.row_pairs ? H : H / 2;
+    const int64_t items = int64_t(d.n_pair_tiles) * B * d.heads_per_item;
+    if (items <= 0 || items > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
+    d.n_items = static_cast<int>(items);
+    const int grid = static_cast<int>(items < g_dev[device].sm_count ? items : g_dev[device].sm_count);
+    intra_fwd_dual_kernel<<<grid, DUAL_THREADS, DUAL_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(d);
+  } else {
+    intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return INTRA_OK;
@@ -235,6 +257,34 @@ int intra_b200_visited_host(int family, int pattern, int S, int param, uint8_t* 
         if (kt >= S) return INTRA_ERR_KERNEL;
         uint8_t* c = counts + size_t(token) * S + kt;
         if (*c < 255) ++*c;
+      }
+    }
+  }
+  return INTRA_OK;
+}
+
+int intra_b200_visited_pairs_host(int family, int pattern, int S, int param, uint8_t* counts) {
+  if (!counts) return INTRA_ERR_BAD_ARG;
+  Problem prob;
+  int rc = problem_from(family, pattern, S, param, &prob);
+  if (rc != INTRA_OK) return rc;
+  const int n = n_pair_tiles(prob, 1);
+  if (n <= 0) return INTRA_ERR_UNSUPPORTED;
+  for (int idx = 0; idx < n; ++idx) {
+    const PairTile pt = make_pair(prob, 1, idx);
+    for (int s = 0; s < 2; ++s) {
+      for (int r = 0; r < TILE_M; ++r) {
+        int token, lo, hi;
+        pair_q_row(prob, pt, s, r, &token, &lo, &hi);
+        if (token < 0) continue;
+        if (token >= S || lo < 0 || hi >= pt.kv.n_kv_tiles * TILE_N) return INTRA_ERR_KERNEL;
+        for (int u = lo; u <= hi; ++u) {
+          const int kt = key_token(prob, pt.kv, u);
+          if (kt < 0) continue;
+          if (kt >= S) return INTRA_ERR_KERNEL;
+          uint8_t* c = counts + size_t(token) * S + kt;
+          if (*c < 255) ++*c;
+        }
       }
     }
   }

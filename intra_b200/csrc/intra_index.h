@@ -272,4 +272,86 @@ INTRA_HD int key_token(const Problem& p, const Tile& t, int u) {
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Pair tiles: two query sub-tiles that share one key-slot list, so that one K / V tile in shared
+// memory feeds 256 query rows.
+//
+//   head pairs (row_pairs == 0): both sub-tiles are the same Tile; the caller gives them two query
+//       heads of one KV-head group (grouped-query attention).
+//   row pairs  (row_pairs == 1): the sub-tiles are two different Tiles of one head whose keys
+//       coincide or nest: consecutive tiles of a Scatter / Gather-1 group, of the window sequence,
+//       or of an image-Scatter group. The shared key list is the union; each sub-tile's [lo, hi]
+//       is shifted into the union's slot numbering (only the window pattern needs a shift).
+//       Gather-0 has no two tiles with nested keys and is not paired.
+struct PairTile {
+  Tile sub[2];     // sub-tile with n_kv_tiles == 0 is absent (all its rows are padding)
+  Tile kv;         // key-slot map of the pair; kv.n_kv_tiles key tiles are processed
+  int shift[2];    // added to sub[s]'s lo / hi to express them in kv's slot numbering
+};
+
+INTRA_HD int n_pair_tiles(const Problem& p, int row_pairs) {
+  if (!row_pairs) return p.n_tiles;
+  switch (p.kind) {
+    case KIND_LLM_SCATTER:
+    case KIND_LLM_GATHER1: return ceil_div(p.tiles_m, 2) * p.G;
+    case KIND_LLM_WINDOW: return ceil_div(p.n_tiles, 2);
+    case KIND_IMG_SCATTER: return ceil_div(p.tiles_m, 2) * IMG_GROUPS;
+    default: return 0;
+  }
+}
+
+// Pair tile `idx` in [0, n_pair_tiles), heaviest first.
+INTRA_HD PairTile make_pair(const Problem& p, int row_pairs, int idx) {
+  PairTile pt;
+  pt.shift[0] = pt.shift[1] = 0;
+  if (!row_pairs) {
+    pt.sub[0] = pt.sub[1] = pt.kv = make_tile(p, idx);
+    return pt;
+  }
+  int idx_first = -1, idx_second = -1;     // first = earlier rows / fewer keys
+  switch (p.kind) {
+    case KIND_LLM_SCATTER:
+    case KIND_LLM_GATHER1: {
+      const int g = idx % p.G, mp = idx / p.G;
+      idx_second = (2 * mp) * p.G + g;
+      if (2 * mp + 1 < p.tiles_m) idx_first = (2 * mp + 1) * p.G + g;
+      break;
+    }
+    case KIND_LLM_WINDOW:
+      idx_second = 2 * idx;
+      if (2 * idx + 1 < p.n_tiles) idx_first = 2 * idx + 1;
+      break;
+    case KIND_IMG_SCATTER: {
+      const int g = idx % IMG_GROUPS, mp = idx / IMG_GROUPS;
+      idx_first = (2 * mp) * IMG_GROUPS + g;
+      if (2 * mp + 1 < p.tiles_m) idx_second = (2 * mp + 1) * IMG_GROUPS + g;
+      break;
+    }
+    default: break;
+  }
+  Tile none = make_tile(p, 0);
+  none.n_kv_tiles = 0; none.nq = 0; none.nk = 0;
+  pt.sub[0] = idx_first >= 0 ? make_tile(p, idx_first) : none;
+  pt.sub[1] = idx_second >= 0 ? make_tile(p, idx_second) : none;
+  const bool has0 = pt.sub[0].n_kv_tiles > 0, has1 = pt.sub[1].n_kv_tiles > 0;
+  pt.kv = has1 ? pt.sub[1] : pt.sub[0];
+  if (p.kind == KIND_LLM_WINDOW && has0 && has1) {
+    pt.kv.kbase = pt.sub[0].kbase;                                  // earlier rows start earlier
+    pt.kv.nk = pt.sub[1].kbase + pt.sub[1].nk - pt.kv.kbase;
+    pt.kv.n_kv_tiles = ceil_div(pt.kv.nk, TILE_N);
+    pt.shift[1] = pt.sub[1].kbase - pt.kv.kbase;
+  }
+  if (!has0 && !has1) pt.kv.n_kv_tiles = 0;
+  return pt;
+}
+
+// q_row of sub-tile s of a pair, with lo / hi in the pair's slot numbering.
+INTRA_HD void pair_q_row(const Problem& p, const PairTile& pt, int s, int r, int* token, int* lo, int* hi) {
+  if (pt.sub[s].n_kv_tiles == 0) { *token = -1; *lo = 0; *hi = pt.kv.nk - 1; return; }
+  q_row(p, pt.sub[s], r, token, lo, hi);
+  if (*token < 0) { *lo = 0; *hi = pt.kv.nk - 1; return; }
+  *lo += pt.shift[s];
+  *hi += pt.shift[s];
+}
+
 }  // namespace intra

@@ -48,3 +48,17 @@ def test_unsupported_shapes_are_rejected(lib):
     assert lib.intra_b200_visited_host(1, 0, 512 + 64, 8, buf.ctypes.data) == -2   # width too small
     assert lib.intra_b200_visited_host(1, 4, 512 + 64 * 64 + 1, 64, buf.ctypes.data) == -2
     assert lib.intra_b200_visited_host(0, 0, 4, 8, buf.ctypes.data) == -2        # more groups than tokens
+
+
+@pytest.mark.parametrize("case", [c for c in MASK_CASES if c["pattern"] != "gather0"], ids=_util.case_id)
+def test_row_pair_visited_set_equals_mask(lib, case):
+    """The decomposition into pairs of row tiles sharing their key tiles visits the same set."""
+    S = case["S"]
+    counts = np.zeros((S, S), dtype=np.uint8)
+    rc = lib.intra_b200_visited_pairs_host(_util.FAMILY[case["family"]],
+                                           _util.PATTERN_ID[(case["family"], case["pattern"])], S,
+                                           _util.case_param(case), counts.ctypes.data)
+    assert rc == 0
+    assert counts.max() <= 1
+    mask = oracle.build_mask(case["family"], case["pattern"], S, **_util.case_kwargs(case))
+    assert np.array_equal(counts.view(bool), mask)
