@@ -18,8 +18,19 @@
 // (csrc/flash_attn/src/flash_fwd_kernel.h:3970-6158) for every pattern whose tiles pair up.
 #pragma once
 #include "attn_kernel.cuh"
+#include "tma_maps.h"
 
 namespace intra {
+
+// Optional cycle-stamp tracing of CTA 0's first item (built only with -DINTRA_TRACE, for bring-up):
+// trace[(role * 64 + (iteration & 63)) * 8 + event] = clock64().
+#ifdef INTRA_TRACE
+__device__ long long g_trace[4 * 64 * 8];
+#define INTRA_TRACE_EV(cond, role, iter, ev) \
+  do { if ((cond) && blockIdx.x == 0 && seq == 0 && (iter) < 64) g_trace[((role) * 64 + (iter)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define INTRA_TRACE_EV(cond, role, iter, ev) do {} while (0)
+#endif
 
 constexpr int DUAL_THREADS = 512;
 constexpr int KV_STAGES = 2;
@@ -32,7 +43,25 @@ struct DualParams {
   int n_pair_tiles;     // pair tiles per (batch, head or head pair)
   int heads_per_item;   // row_pairs ? H : H / 2  (number of items per pair tile and batch)
   int n_items;          // n_pair_tiles * B * heads_per_item
+  int use_tma;          // tiles are fetched as TMA boxes (tma_maps.h) instead of cp.async row gathers
+  TmaMaps maps;
 };
+
+// Fetch the 128 rows starting at `start` of tile `t` into the swizzled tile at `dst` (two boxes, one
+// per half of the head dim), completion counted on `bar`.
+__device__ __forceinline__ void tma_fetch_tile(const Problem& prob, const Tile& t, int start, bool text, int head,
+                                               int batch, const CUtensorMap* main_map, const CUtensorMap* text_map,
+                                               uint32_t dst, uint64_t* bar) {
+  int c[5];
+  const int is_text = tma_box_coords(prob, t, start, text, head, batch, c);
+  const bool rank4 = is_text || prob.kind == KIND_LLM_WINDOW;
+  const CUtensorMap* m = is_text ? text_map : main_map;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    if (rank4) ptx::tma_load_4d(dst + half * HALF_BYTES, m, bar, half * 64, c[1], c[2], c[3]);
+    else ptx::tma_load_5d(dst + half * HALF_BYTES, m, bar, half * 64, c[1], c[2], c[3], c[4]);
+  }
+}
 
 struct DualItem {
   PairTile pt;
@@ -57,7 +86,7 @@ __device__ __forceinline__ DualItem dual_decode(const DualParams& p, int item) {
   return it;
 }
 
-__global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const DualParams p) {
+__global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const __grid_constant__ DualParams p) {
   extern __shared__ uint8_t smem_raw[];
   // barriers: 0 q_full, 1 q_empty, 2-3 k_full, 4-5 k_empty, 6-7 v_full, 8-9 v_empty,
   //           10-11 s_full[s], 12-13 p_full[s], 14-15 o_done[s], 16 drain
@@ -92,12 +121,13 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
 
   if (tid == 0) {
     abort_flag = 0;
-    ptx::mbar_init(q_full, 128);
+    const uint32_t producers = p.use_tma ? 1 : 128;       // one TMA-issuing thread, or every loader thread
+    ptx::mbar_init(q_full, producers);
     ptx::mbar_init(q_empty, 1);
     for (int j = 0; j < KV_STAGES; ++j) {
-      ptx::mbar_init(&k_full[j], 128);
+      ptx::mbar_init(&k_full[j], producers);
       ptx::mbar_init(&k_empty[j], 1);
-      ptx::mbar_init(&v_full[j], 128);
+      ptx::mbar_init(&v_full[j], producers);
       ptx::mbar_init(&v_empty[j], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -150,11 +180,13 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
         ok = ptx::mbar_wait(my_s_full, it & 1, abort_p);
         if (!ok) { if (*abort_p == 1) *abort_p = 11 + s_idx; break; }
         ptx::tc_fence_after();
+        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 0);
 
         float s[TILE_N];
 #pragma unroll
         for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_addr + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
         ptx::tmem_wait_ld();
+        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 1);
 
         const int u0 = n * TILE_N;
         if (lo > u0 || hi < u0 + TILE_N - 1) {            // this row's interval does not cover the tile
@@ -168,6 +200,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
 #pragma unroll
         for (int c = 1; c < TILE_N; ++c) tmax = fmaxf(tmax, s[c]);
         const float m_new = fmaxf(m_run, tmax);
+        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 2);
         const bool grow = (m_new - m_run) * scale_log2 > RESCALE_THRESHOLD;
         float alpha = 1.f;
         if (grow) {
@@ -204,9 +237,11 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
           ptx::tmem_st16(s_addr + c4 * 16, pk);
         }
         l_run += lsum;
+        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 3);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(my_p_full);
+        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 4);
       }
       if (!ok) break;
 
@@ -247,6 +282,58 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
     bool ok = true;
     int n_done = 0;
 
+    if (p.use_tma) {
+      // ---- one thread drives the TMA unit; the other loader threads have nothing to do ----------
+      if (warp == 8 && lane == 0) {
+        ptx::prefetch_tensormap(&p.maps.q_main);
+        ptx::prefetch_tensormap(&p.maps.k_main);
+        ptx::prefetch_tensormap(&p.maps.v_main);
+        for (int seq = 0; ok; ++seq) {
+          const int item = dual_item_index(seq, cta, n_cta);
+          if (item >= p.n_items) break;
+          const DualItem di = dual_decode(p, item);
+          const int n_kv = di.pt.kv.n_kv_tiles;
+          if (n_kv == 0) continue;
+          if (n_done > 0) {
+            ok = ptx::mbar_wait(q_empty, (n_done - 1) & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 21; break; }
+          }
+          ptx::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+          {
+            // an absent sub-tile (odd tile count) is fed the other one's rows; its results are dropped
+            const Tile& t0 = di.pt.sub[0].n_kv_tiles > 0 ? di.pt.sub[0] : di.pt.sub[1];
+            const Tile& t1 = di.pt.sub[1].n_kv_tiles > 0 ? di.pt.sub[1] : di.pt.sub[0];
+            int start; bool text;
+            tma_q_start(t0, &start, &text);
+            tma_fetch_tile(p.f.prob, t0, start, text, di.h0, di.b, &p.maps.q_main, &p.maps.q_text, q_smem0, q_full);
+            tma_q_start(t1, &start, &text);
+            tma_fetch_tile(p.f.prob, t1, start, text, di.h1, di.b, &p.maps.q_main, &p.maps.q_text,
+                           q_smem0 + TILE_BYTES, q_full);
+          }
+          for (int n = 0; n < n_kv && ok; ++n, ++kc) {
+            const int stage = kc % KV_STAGES;
+            const uint32_t use = kc / KV_STAGES;
+            int start; bool text;
+            tma_kv_start(di.pt.kv, n, &start, &text);
+            if (use > 0) {
+              ok = ptx::mbar_wait(&k_empty[stage], (use - 1) & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 22; break; }
+            }
+            ptx::mbar_arrive_expect_tx(&k_full[stage], TILE_BYTES);
+            tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.k_main, &p.maps.k_text,
+                           k_smem0 + stage * TILE_BYTES, &k_full[stage]);
+            if (use > 0) {
+              ok = ptx::mbar_wait(&v_empty[stage], (use - 1) & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 23; break; }
+            }
+            ptx::mbar_arrive_expect_tx(&v_full[stage], TILE_BYTES);
+            tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.v_main, &p.maps.v_text,
+                           v_smem0 + stage * TILE_BYTES, &v_full[stage]);
+          }
+          ++n_done;
+        }
+      }
+    } else
     for (int seq = 0; ok; ++seq) {
       const int item = dual_item_index(seq, cta, n_cta);
       if (item >= p.n_items) break;
@@ -281,10 +368,12 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
         int tokens[TILE_N / 8];
 #pragma unroll
         for (int ps = 0; ps < TILE_N / 8; ++ps) tokens[ps] = key_token(p.f.prob, di.pt.kv, n * TILE_N + ps * 8 + rsub);
+        INTRA_TRACE_EV(lt == 0, 3, n, 4);
         if (use > 0) {
           ok = ptx::mbar_wait(&k_empty[stage], (use - 1) & 1, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 22; break; }
         }
+        INTRA_TRACE_EV(lt == 0, 3, n, 0);
         const uint32_t kdst = k_smem0 + stage * TILE_BYTES;
 #pragma unroll
         for (int ps = 0; ps < TILE_N / 8; ++ps) {
@@ -294,10 +383,12 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
           ptx::cp_async_16(kdst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
         }
         ptx::cp_async_mbar_arrive_noinc(&k_full[stage]);
+        INTRA_TRACE_EV(lt == 0, 3, n, 1);
         if (use > 0) {
           ok = ptx::mbar_wait(&v_empty[stage], (use - 1) & 1, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 23; break; }
         }
+        INTRA_TRACE_EV(lt == 0, 3, n, 2);
         const uint32_t vdst = v_smem0 + stage * TILE_BYTES;
 #pragma unroll
         for (int ps = 0; ps < TILE_N / 8; ++ps) {
@@ -307,6 +398,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
           ptx::cp_async_16(vdst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
         }
         ptx::cp_async_mbar_arrive_noinc(&v_full[stage]);
+        INTRA_TRACE_EV(lt == 0, 3, n, 3);
       }
       ++n_done;
     }
@@ -338,6 +430,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
           if (!ok) { if (*abort_p == 1) *abort_p = 32; break; }
           ptx::fence_proxy_async_smem();
           ptx::tc_fence_after();
+          INTRA_TRACE_EV(lane == 0, 0, n, 0);
           const uint32_t k_smem = k_smem0 + stage * TILE_BYTES;
           if (lane == 0) {
             issue_qk(q_smem0, k_smem, tmem + 0);
@@ -348,6 +441,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
             ok = ptx::mbar_wait(&p_full[1], it1 & 1, abort_p);
             if (!ok) { if (*abort_p == 1) *abort_p = 33; break; }
             ptx::tc_fence_after();
+            INTRA_TRACE_EV(lane == 0, 0, n, 1);
             if (lane == 0) {
               issue_pv(tmem + 128, v_smem0 + pend_stage * TILE_BYTES, tmem + 384, pend_acc != 0);
               ptx::mma_commit(&o_done[1]);
@@ -364,12 +458,15 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const D
             if (n == n_kv - 1) ptx::mma_commit(q_empty);
           }
           __syncwarp();
+          INTRA_TRACE_EV(lane == 0, 0, n, 2);
           ok = ptx::mbar_wait(&v_full[stage], par, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 34; break; }
           ptx::fence_proxy_async_smem();
+          INTRA_TRACE_EV(lane == 0, 0, n, 3);
           ok = ptx::mbar_wait(&p_full[0], it0 & 1, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 35; break; }
           ptx::tc_fence_after();
+          INTRA_TRACE_EV(lane == 0, 0, n, 4);
           if (lane == 0) {
             issue_pv(tmem + 0, v_smem0 + stage * TILE_BYTES, tmem + 256, n > 0);
             ptx::mma_commit(&o_done[0]);

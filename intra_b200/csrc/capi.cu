@@ -4,6 +4,7 @@
 // owns every tensor, this file only validates, fills the parameter block and launches.
 #include "../../include/intra_b200.h"
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cmath>
@@ -101,6 +102,79 @@ int problem_from(int family, int pattern, int S, int param, Problem* prob) {
   return INTRA_OK;
 }
 
+// ---- tensor maps ------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime, so the library does not link against libcuda.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult r;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &r) != cudaSuccess ||
+        r != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+bool encode_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+                const cuuint32_t* box, const cuuint32_t* estr) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  for (int i = 0; i < rank; ++i)
+    if (dims[i] == 0 || dims[i] > 0xffffffffull || box[i] == 0 || box[i] > 256) return false;
+  for (int i = 0; i + 1 < rank; ++i)
+    if (strides_bytes[i] == 0 || strides_bytes[i] % 16 != 0 || strides_bytes[i] >= (1ull << 40)) return false;
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides_bytes, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The views of tma_maps.h for one (batch, token, head, 128) tensor with `heads` heads.
+bool build_maps(const Problem& p, const __nv_bfloat16* ptr, const TensorView& tv, int heads, int B, CUtensorMap* main_map,
+                CUtensorMap* text_map) {
+  const cuuint64_t ss = cuuint64_t(tv.ss) * 2, sh = cuuint64_t(tv.sh) * 2, sb = cuuint64_t(tv.sb) * 2;
+  if (tv.ss <= 0 || tv.sh <= 0 || tv.sb <= 0) return false;
+  const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+  switch (p.kind) {
+    case KIND_LLM_SCATTER: {
+      const cuuint64_t dims[5] = {128, cuuint64_t(p.G), cuuint64_t(p.S / p.G), cuuint64_t(heads), cuuint64_t(B)};
+      const cuuint64_t str[4] = {ss, ss * p.G, sh, sb};
+      const cuuint32_t box[5] = {64, 1, 128, 1, 1};
+      return encode_map(main_map, ptr, 5, dims, str, box, ones);
+    }
+    case KIND_LLM_GATHER1: {
+      const cuuint64_t span = cuuint64_t(p.G) * p.G;
+      const cuuint64_t dims[5] = {128, span, cuuint64_t(p.S) / span, cuuint64_t(heads), cuuint64_t(B)};
+      const cuuint64_t str[4] = {ss, ss * span, sh, sb};
+      const cuuint32_t box[5] = {64, cuuint32_t(p.G), cuuint32_t(TILE_M / p.G), 1, 1};
+      return encode_map(main_map, ptr, 5, dims, str, box, ones);
+    }
+    case KIND_LLM_WINDOW: {
+      const cuuint64_t dims[4] = {128, cuuint64_t(p.S), cuuint64_t(heads), cuuint64_t(B)};
+      const cuuint64_t str[3] = {ss, sh, sb};
+      const cuuint32_t box[4] = {64, 128, 1, 1};
+      return encode_map(main_map, ptr, 4, dims, str, box, ones);
+    }
+    case KIND_IMG_SCATTER: {
+      const cuuint64_t dims[5] = {128, cuuint64_t(p.W), cuuint64_t(p.W), cuuint64_t(heads), cuuint64_t(B)};
+      const cuuint64_t str[4] = {ss, ss * p.W, sh, sb};
+      const cuuint32_t box[5] = {64, cuuint32_t(p.W), cuuint32_t(2 * (TILE_M / (p.W / 4))), 1, 1};
+      const cuuint32_t estr[5] = {1, 4, 2, 1, 1};
+      if (!encode_map(main_map, ptr + int64_t(TEXT_LEN) * tv.ss, 5, dims, str, box, estr)) return false;
+      const cuuint64_t tdims[4] = {128, TEXT_LEN, cuuint64_t(heads), cuuint64_t(B)};
+      const cuuint64_t tstr[3] = {ss, sh, sb};
+      const cuuint32_t tbox[4] = {64, 128, 1, 1};
+      return encode_map(text_map, ptr, 4, tdims, tstr, tbox, ones);
+    }
+    default:
+      return false;
+  }
+}
+
 // ---- scratch for intra_b200_fwd_llm_noalloc -------------------------------------------------------
 // The attention kernel's only scratch is the status word it reports to. For callers that must not
 // allocate, that word lives in this fixed array, which every GPU that loads the library holds until
@@ -179,6 +253,11 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
     const int64_t items = int64_t(d.n_pair_tiles) * B * d.heads_per_item;
     if (items <= 0 || items > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
     d.n_items = static_cast<int>(items);
+    static const bool no_tma = [] { const char* v = std::getenv("INTRA_B200_NO_TMA"); return v && v[0] == '1'; }();
+    d.use_tma = !no_tma && tma_supported(p.prob) &&
+                build_maps(p.prob, p.q, p.qs, H, B, &d.maps.q_main, &d.maps.q_text) &&
+                build_maps(p.prob, p.k, p.ks, Hkv, B, &d.maps.k_main, &d.maps.k_text) &&
+                build_maps(p.prob, p.v, p.vs, Hkv, B, &d.maps.v_main, &d.maps.v_text);
     const int grid = static_cast<int>(items < g_dev[device].sm_count ? items : g_dev[device].sm_count);
     intra_fwd_dual_kernel<<<grid, DUAL_THREADS, DUAL_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(d);
   } else {
