@@ -66,25 +66,38 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
   return (chunk >> 3) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
-// S[128 x 128] = A[128 x 128] * B[128 x 128]^T, both K-major tiles: 8 MMAs of K = 16.
-__device__ __forceinline__ void issue_qk(uint32_t q_smem, uint32_t k_smem, uint32_t s_tmem) {
+// Descriptor of a whole swizzled tile as a K-major operand (Q, or K for QK^T) and as an MN-major one
+// (V for PV). The per-MMA descriptors differ from these only in the start-address field, so the issuing
+// thread adds a constant per step instead of rebuilding them.
+__device__ __forceinline__ uint64_t tile_desc_kmajor(uint32_t smem) { return ptx::smem_desc_sw128(smem, 16, 1024); }
+__device__ __forceinline__ uint64_t tile_desc_mnmajor(uint32_t smem) { return ptx::smem_desc_sw128(smem, HALF_BYTES, 1024); }
+
+// S[128 x 128] = A[128 x 128] * B[128 x 128]^T, both K-major tiles: 8 MMAs of K = 16. Step s reads the
+// 32-byte slice s % 4 of half s / 4 of each row; descriptor addresses count 16-byte units.
+__device__ __forceinline__ void issue_qk_desc(uint64_t q_desc, uint64_t k_desc, uint32_t s_tmem) {
   constexpr uint32_t idesc = ptx::idesc_bf16_f32(TILE_M, TILE_N, 0, 0);
 #pragma unroll
   for (int s = 0; s < HEAD_DIM / 16; ++s) {
-    const uint32_t off = (s >> 2) * HALF_BYTES + (s & 3) * 32;
-    ptx::mma_ss(s_tmem, ptx::smem_desc_sw128(q_smem + off, 16, 1024), ptx::smem_desc_sw128(k_smem + off, 16, 1024),
-                idesc, s > 0 ? 1u : 0u);
+    const uint64_t off = uint64_t(((s >> 2) * HALF_BYTES + (s & 3) * 32) >> 4);
+    if (s == 0) ptx::mma_ss_first(s_tmem, q_desc + off, k_desc + off, idesc);
+    else ptx::mma_ss_acc(s_tmem, q_desc + off, k_desc + off, idesc);
   }
 }
+__device__ __forceinline__ void issue_qk(uint32_t q_smem, uint32_t k_smem, uint32_t s_tmem) {
+  issue_qk_desc(tile_desc_kmajor(q_smem), tile_desc_kmajor(k_smem), s_tmem);
+}
 // O[128 x 128] (+)= P[128 x 128 keys] * V[128 keys x 128]: A from tensor memory (bf16 pairs, 8
-// columns per 16 keys), B = V tile read MN-major (head dim contiguous): 8 MMAs of K = 16 keys.
-__device__ __forceinline__ void issue_pv(uint32_t p_tmem, uint32_t v_smem, uint32_t o_tmem, bool accumulate) {
+// columns per 16 keys), B = V tile read MN-major (head dim contiguous): 8 MMAs of K = 16 keys, each
+// 16 keys = 2048 bytes further into the tile.
+__device__ __forceinline__ void issue_pv_desc(uint32_t p_tmem, uint64_t v_desc, uint32_t o_tmem, bool accumulate) {
   constexpr uint32_t idesc = ptx::idesc_bf16_f32(TILE_M, HEAD_DIM, 0, 1);
+  if (accumulate) ptx::mma_ts_acc(o_tmem, p_tmem, v_desc, idesc);
+  else ptx::mma_ts_first(o_tmem, p_tmem, v_desc, idesc);
 #pragma unroll
-  for (int s = 0; s < TILE_N / 16; ++s) {
-    ptx::mma_ts(o_tmem, p_tmem + s * 8, ptx::smem_desc_sw128(v_smem + s * 2048, HALF_BYTES, 1024), idesc,
-                (accumulate || s > 0) ? 1u : 0u);
-  }
+  for (int s = 1; s < TILE_N / 16; ++s) ptx::mma_ts_acc(o_tmem, p_tmem + s * 8, v_desc + uint64_t(s * (2048 >> 4)), idesc);
+}
+__device__ __forceinline__ void issue_pv(uint32_t p_tmem, uint32_t v_smem, uint32_t o_tmem, bool accumulate) {
+  issue_pv_desc(p_tmem, tile_desc_mnmajor(v_smem), o_tmem, accumulate);
 }
 
 __global__ void __launch_bounds__(FWD_THREADS, 2) intra_fwd_kernel(const FwdParams p) {
@@ -322,7 +335,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) intra_fwd_kernel(const FwdPara
         ok = ptx::mbar_wait(k_full, n & 1, abort_p);
         if (!ok) { if (*abort_p == 1) *abort_p = 32; break; }
         ptx::tc_fence_after();
-        if (lane == 0) {
+        if (ptx::elect_one()) {
           issue_qk(q_smem, k_smem, tmem + TMEM_S);
           ptx::mma_commit(k_empty);
           ptx::mma_commit(s_full);
@@ -333,7 +346,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) intra_fwd_kernel(const FwdPara
         ok = ptx::mbar_wait(v_full, n & 1, abort_p);
         if (!ok) { if (*abort_p == 1) *abort_p = 34; break; }
         ptx::tc_fence_after();
-        if (lane == 0) {
+        if (ptx::elect_one()) {
           issue_pv(tmem + TMEM_S, v_smem, tmem + TMEM_O, n > 0);
           ptx::mma_commit(v_empty);
           ptx::mma_commit(o_done);
@@ -341,7 +354,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) intra_fwd_kernel(const FwdPara
         __syncwarp();
       }
       if (!ok) {                                          // let MMAs in flight finish before TMEM is freed
-        if (lane == 0) ptx::mma_commit(drain);
+        if (ptx::elect_one()) ptx::mma_commit(drain);
         __syncwarp();
         int dummy = 0;
         ptx::mbar_wait(drain, 0, &dummy, 100);

@@ -14,10 +14,17 @@
 // Items are dealt to CTAs heaviest first in boustrophedon order, which needs no counters in global
 // memory. Every wait is bounded; see attn_kernel.cuh for the abort protocol, which is the same.
 //
+// A tcgen05.commit costs the tensor pipe about as much as one MMA, so only two are issued per key tile:
+// after QK0 (S0 ready) and after QK1 (S1 ready). Because the pipe completes in issue order the second
+// one also tells the loaders that the K stage of that tile, the V stage of the tile before it and - on
+// a tile's last key tile - the Q buffers may be overwritten; it alternates between two barriers so
+// that waiters a tile ahead or behind can never confuse phases. O is signalled once per item.
+//
 // Replaces, like attn_kernel.cuh, the reference's compute_attn_1rowblock_* kernels
 // (csrc/flash_attn/src/flash_fwd_kernel.h:3970-6158) for every pattern whose tiles pair up.
 #pragma once
 #include "attn_kernel.cuh"
+#include "softmax.cuh"
 #include "tma_maps.h"
 
 namespace intra {
@@ -88,9 +95,9 @@ __device__ __forceinline__ DualItem dual_decode(const DualParams& p, int item) {
 
 __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const __grid_constant__ DualParams p) {
   extern __shared__ uint8_t smem_raw[];
-  // barriers: 0 q_full, 1 q_empty, 2-3 k_full, 4-5 k_empty, 6-7 v_full, 8-9 v_empty,
-  //           10-11 s_full[s], 12-13 p_full[s], 14-15 o_done[s], 16 drain
-  __shared__ uint64_t bars[17];
+  // barriers: 0 q_full, 1-2 k_full, 3-4 v_full, 5 s0_full, 6-7 s1_full[stage], 8-9 p_full[s],
+  //           10-11 o_done[s], 12 drain
+  __shared__ uint64_t bars[13];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
 
@@ -104,15 +111,13 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
   __syncthreads();
 
   uint64_t* q_full = &bars[0];
-  uint64_t* q_empty = &bars[1];
-  uint64_t* k_full = &bars[2];
-  uint64_t* k_empty = &bars[4];
-  uint64_t* v_full = &bars[6];
-  uint64_t* v_empty = &bars[8];
-  uint64_t* s_full = &bars[10];
-  uint64_t* p_full = &bars[12];
-  uint64_t* o_done = &bars[14];
-  uint64_t* drain = &bars[16];
+  uint64_t* k_full = &bars[1];
+  uint64_t* v_full = &bars[3];
+  uint64_t* s0_full = &bars[5];     // QK0 of a key tile has completed
+  uint64_t* s1_full = &bars[6];     // [key tile & 1]: QK1 of that key tile (and everything issued before it)
+  uint64_t* p_full = &bars[8];
+  uint64_t* o_done = &bars[10];     // last PV of an item, per sub-tile
+  uint64_t* drain = &bars[12];
 
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem0 = smem_base;                                 // Q sub-tile s at + s * TILE_BYTES
@@ -123,15 +128,13 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
     abort_flag = 0;
     const uint32_t producers = p.use_tma ? 1 : 128;       // one TMA-issuing thread, or every loader thread
     ptx::mbar_init(q_full, producers);
-    ptx::mbar_init(q_empty, 1);
     for (int j = 0; j < KV_STAGES; ++j) {
       ptx::mbar_init(&k_full[j], producers);
-      ptx::mbar_init(&k_empty[j], 1);
       ptx::mbar_init(&v_full[j], producers);
-      ptx::mbar_init(&v_empty[j], 1);
     }
+    ptx::mbar_init(s0_full, 1);
     for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(&s_full[s], 1);
+      ptx::mbar_init(&s1_full[s], 1);
       ptx::mbar_init(&p_full[s], 128);
       ptx::mbar_init(&o_done[s], 1);
     }
@@ -150,6 +153,14 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
   const int n_cta = gridDim.x;
   const int cta = blockIdx.x;
 
+  // Loader-side waits on the MMA warp's progress (see the note on commits at the top of the file).
+  // Key tile j (counted over the whole CTA) signals s1_full[j & 1]; its phase there has parity (j / 2) & 1.
+#define INTRA_WAIT_TILE_DONE(j, code)                                               \
+  do {                                                                              \
+    ok = ptx::mbar_wait(&s1_full[(j) & 1], ((j) >> 1) & 1, abort_p);                \
+    if (!ok) { if (*abort_p == 1) *abort_p = (code); }                              \
+  } while (0)
+
   if (warp < 8) {
     // ================================ softmax / correction / epilogue ==========================
     ptx::setmaxnreg_inc<192>();
@@ -158,11 +169,11 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
     const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
     const uint32_t s_addr = lane_addr + s_idx * 128;
     const uint32_t o_addr = lane_addr + 256 + s_idx * 128;
-    uint64_t* my_s_full = &s_full[s_idx];
     uint64_t* my_p_full = &p_full[s_idx];
     uint64_t* my_o_done = &o_done[s_idx];
     const float scale_log2 = p.f.scale_log2;
-    uint32_t it = 0;                                      // key tiles processed so far (barrier phases)
+    uint32_t it = 0;                                      // key tiles processed so far by this CTA
+    uint32_t n_done = 0;                                  // items finished
     bool ok = true;
 
     for (int seq = 0; ok; ++seq) {
@@ -177,7 +188,8 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
       float l_run = 0.f;
 
       for (int n = 0; n < n_kv; ++n, ++it) {
-        ok = ptx::mbar_wait(my_s_full, it & 1, abort_p);
+        if (s_idx == 0) ok = ptx::mbar_wait(s0_full, it & 1, abort_p);
+        else ok = ptx::mbar_wait(&s1_full[it & 1], (it >> 1) & 1, abort_p);
         if (!ok) { if (*abort_p == 1) *abort_p = 11 + s_idx; break; }
         ptx::tc_fence_after();
         INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 0);
@@ -196,22 +208,20 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
             if (u < lo || u > hi) s[c] = -CUDART_INF_F;
           }
         }
-        float tmax = s[0];
-#pragma unroll
-        for (int c = 1; c < TILE_N; ++c) tmax = fmaxf(tmax, s[c]);
-        const float m_new = fmaxf(m_run, tmax);
+        const float m_new = fmaxf(m_run, sm::row_max(s));
         INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 2);
+        // Move the running maximum only when the scores outgrow it by 2^8; until then p is merely
+        // scaled by a constant that the final division by the row sum removes.
         const bool grow = (m_new - m_run) * scale_log2 > RESCALE_THRESHOLD;
         float alpha = 1.f;
         if (grow) {
-          alpha = ptx::ex2((m_run - m_new) * scale_log2);
+          alpha = ptx::ex2((m_run - m_new) * scale_log2);  // 0 when m_run is still -inf
           l_run *= alpha;
           m_run = m_new;
         }
         if (n > 0 && __any_sync(0xffffffffu, grow)) {     // rare once the maximum has settled
-          ok = ptx::mbar_wait(my_o_done, (it - 1) & 1, abort_p);   // PV of the previous key tile has landed
-          if (!ok) { if (*abort_p == 1) *abort_p = 13 + s_idx; break; }
-          ptx::tc_fence_after();
+          // The previous key tile's PV was issued before the QK^T whose completion was just waited
+          // for, and the tensor pipe completes in order: O is quiescent here.
 #pragma unroll 1
           for (int c = 0; c < HEAD_DIM / 16; ++c) {
             uint32_t o[16];
@@ -223,20 +233,14 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           }
         }
         const float base = (m_run == -CUDART_INF_F) ? 0.f : m_run * scale_log2;
-        float lsum = 0.f;
+        sm::f2 sum[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
         for (int c4 = 0; c4 < 4; ++c4) {                  // 32 scores -> 16 packed columns of P
           uint32_t pk[16];
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float p0 = ptx::ex2(fmaf(s[c4 * 32 + 2 * c], scale_log2, -base));
-            const float p1 = ptx::ex2(fmaf(s[c4 * 32 + 2 * c + 1], scale_log2, -base));
-            lsum += p0 + p1;
-            pk[c] = ptx::pack_bf16(p0, p1);
-          }
+          sm::exp_chunk(s, c4 * 32, scale_log2, base, pk, sum);
           ptx::tmem_st16(s_addr + c4 * 16, pk);
         }
-        l_run += lsum;
+        l_run += sm::sum4(sum);
         INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 3);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
@@ -245,8 +249,9 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
       }
       if (!ok) break;
 
-      ok = ptx::mbar_wait(my_o_done, (it - 1) & 1, abort_p);       // last PV of this item
+      ok = ptx::mbar_wait(my_o_done, n_done & 1, abort_p);         // last PV of this item
       if (!ok) { if (*abort_p == 1) *abort_p = 15 + s_idx; break; }
+      ++n_done;
       ptx::tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const int h = s_idx ? di.h1 : di.h0;
@@ -276,8 +281,6 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
     // ================================ loaders ===================================================
     ptx::setmaxnreg_dec<64>();
     const int lt = tid - 256;
-    const int chunk = lt & 15;                            // 16-byte chunk of the 256-byte row
-    const int rsub = lt >> 4;                             // row within a pass of 8 rows
     uint32_t kc = 0;                                      // K / V tiles loaded so far (ring position)
     bool ok = true;
     int n_done = 0;
@@ -294,9 +297,9 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           const DualItem di = dual_decode(p, item);
           const int n_kv = di.pt.kv.n_kv_tiles;
           if (n_kv == 0) continue;
-          if (n_done > 0) {
-            ok = ptx::mbar_wait(q_empty, (n_done - 1) & 1, abort_p);
-            if (!ok) { if (*abort_p == 1) *abort_p = 21; break; }
+          if (n_done > 0) {                               // Q buffers: last QK^T of the previous item
+            INTRA_WAIT_TILE_DONE(kc - 1, 21);
+            if (!ok) break;
           }
           ptx::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
           {
@@ -312,19 +315,18 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           }
           for (int n = 0; n < n_kv && ok; ++n, ++kc) {
             const int stage = kc % KV_STAGES;
-            const uint32_t use = kc / KV_STAGES;
             int start; bool text;
             tma_kv_start(di.pt.kv, n, &start, &text);
-            if (use > 0) {
-              ok = ptx::mbar_wait(&k_empty[stage], (use - 1) & 1, abort_p);
-              if (!ok) { if (*abort_p == 1) *abort_p = 22; break; }
+            if (kc >= 2) {                                // K stage: QK1 of key tile kc-2
+              INTRA_WAIT_TILE_DONE(kc - 2, 22);
+              if (!ok) break;
             }
             ptx::mbar_arrive_expect_tx(&k_full[stage], TILE_BYTES);
             tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.k_main, &p.maps.k_text,
                            k_smem0 + stage * TILE_BYTES, &k_full[stage]);
-            if (use > 0) {
-              ok = ptx::mbar_wait(&v_empty[stage], (use - 1) & 1, abort_p);
-              if (!ok) { if (*abort_p == 1) *abort_p = 23; break; }
+            if (kc >= 2) {                                // V stage: PV1 of key tile kc-2, issued before QK1 of kc-1
+              INTRA_WAIT_TILE_DONE(kc - 1, 23);
+              if (!ok) break;
             }
             ptx::mbar_arrive_expect_tx(&v_full[stage], TILE_BYTES);
             tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.v_main, &p.maps.v_text,
@@ -333,84 +335,87 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           ++n_done;
         }
       }
-    } else
-    for (int seq = 0; ok; ++seq) {
-      const int item = dual_item_index(seq, cta, n_cta);
-      if (item >= p.n_items) break;
-      const DualItem di = dual_decode(p, item);
-      const int n_kv = di.pt.kv.n_kv_tiles;
-      if (n_kv == 0) continue;
-      if (n_done > 0) {                                   // Q buffers free once the previous item's last QK^T is done
-        ok = ptx::mbar_wait(q_empty, (n_done - 1) & 1, abort_p);
-        if (!ok) { if (*abort_p == 1) *abort_p = 21; break; }
-      }
-      {
-        const __nv_bfloat16* qb0 = p.f.q + di.b * p.f.qs.sb + di.h0 * p.f.qs.sh + chunk * 8;
-        const __nv_bfloat16* qb1 = p.f.q + di.b * p.f.qs.sb + di.h1 * p.f.qs.sh + chunk * 8;
+    } else {
+      // ---- cp.async row gathers by all 128 loader threads (ragged shapes) ------------------------
+      const int chunk = lt & 15;                          // 16-byte chunk of the 256-byte row
+      const int rsub = lt >> 4;                           // row within a pass of 8 rows
+      for (int seq = 0; ok; ++seq) {
+        const int item = dual_item_index(seq, cta, n_cta);
+        if (item >= p.n_items) break;
+        const DualItem di = dual_decode(p, item);
+        const int n_kv = di.pt.kv.n_kv_tiles;
+        if (n_kv == 0) continue;
+        if (n_done > 0) {
+          INTRA_WAIT_TILE_DONE(kc - 1, 21);
+          if (!ok) break;
+        }
+        {
+          const __nv_bfloat16* qb0 = p.f.q + di.b * p.f.qs.sb + di.h0 * p.f.qs.sh + chunk * 8;
+          const __nv_bfloat16* qb1 = p.f.q + di.b * p.f.qs.sb + di.h1 * p.f.qs.sh + chunk * 8;
 #pragma unroll 4
-        for (int ps = 0; ps < TILE_M / 8; ++ps) {
-          const int row = ps * 8 + rsub;
-          int token, lo, hi;
-          pair_q_row(p.f.prob, di.pt, 0, row, &token, &lo, &hi);
-          const void* src = token >= 0 ? static_cast<const void*>(qb0 + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
-          ptx::cp_async_16(q_smem0 + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
-          if (p.row_pairs) pair_q_row(p.f.prob, di.pt, 1, row, &token, &lo, &hi);
-          src = token >= 0 ? static_cast<const void*>(qb1 + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
-          ptx::cp_async_16(q_smem0 + TILE_BYTES + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+          for (int ps = 0; ps < TILE_M / 8; ++ps) {
+            const int row = ps * 8 + rsub;
+            int token, lo, hi;
+            pair_q_row(p.f.prob, di.pt, 0, row, &token, &lo, &hi);
+            const void* src = token >= 0 ? static_cast<const void*>(qb0 + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
+            ptx::cp_async_16(q_smem0 + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+            if (p.row_pairs) pair_q_row(p.f.prob, di.pt, 1, row, &token, &lo, &hi);
+            src = token >= 0 ? static_cast<const void*>(qb1 + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
+            ptx::cp_async_16(q_smem0 + TILE_BYTES + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+          }
+          ptx::cp_async_mbar_arrive_noinc(q_full);
         }
-        ptx::cp_async_mbar_arrive_noinc(q_full);
+        const __nv_bfloat16* kb = p.f.k + di.b * p.f.ks.sb + di.hk * p.f.ks.sh + chunk * 8;
+        const __nv_bfloat16* vb = p.f.v + di.b * p.f.vs.sb + di.hk * p.f.vs.sh + chunk * 8;
+        const Tile kv = di.pt.kv;
+        for (int n = 0; n < n_kv && ok; ++n, ++kc) {
+          const int stage = kc % KV_STAGES;
+          int tokens[TILE_N / 8];
+#pragma unroll
+          for (int ps = 0; ps < TILE_N / 8; ++ps) tokens[ps] = key_token(p.f.prob, kv, n * TILE_N + ps * 8 + rsub);
+          if (kc >= 2) {
+            INTRA_WAIT_TILE_DONE(kc - 2, 22);
+            if (!ok) break;
+          }
+          const uint32_t kdst = k_smem0 + stage * TILE_BYTES;
+#pragma unroll
+          for (int ps = 0; ps < TILE_N / 8; ++ps) {
+            const int row = ps * 8 + rsub;
+            const int token = tokens[ps];
+            const void* src = token >= 0 ? static_cast<const void*>(kb + int64_t(token) * p.f.ks.ss) : static_cast<const void*>(p.f.k);
+            ptx::cp_async_16(kdst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+          }
+          ptx::cp_async_mbar_arrive_noinc(&k_full[stage]);
+          if (kc >= 2) {
+            INTRA_WAIT_TILE_DONE(kc - 1, 23);
+            if (!ok) break;
+          }
+          const uint32_t vdst = v_smem0 + stage * TILE_BYTES;
+#pragma unroll
+          for (int ps = 0; ps < TILE_N / 8; ++ps) {
+            const int row = ps * 8 + rsub;
+            const int token = tokens[ps];
+            const void* src = token >= 0 ? static_cast<const void*>(vb + int64_t(token) * p.f.vs.ss) : static_cast<const void*>(p.f.v);
+            ptx::cp_async_16(vdst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+          }
+          ptx::cp_async_mbar_arrive_noinc(&v_full[stage]);
+        }
+        ++n_done;
       }
-      const __nv_bfloat16* kb = p.f.k + di.b * p.f.ks.sb + di.hk * p.f.ks.sh + chunk * 8;
-      const __nv_bfloat16* vb = p.f.v + di.b * p.f.vs.sb + di.hk * p.f.vs.sh + chunk * 8;
-      for (int n = 0; n < n_kv && ok; ++n, ++kc) {
-        const int stage = kc % KV_STAGES;
-        const uint32_t use = kc / KV_STAGES;              // how often this stage has been filled before
-        int tokens[TILE_N / 8];
-#pragma unroll
-        for (int ps = 0; ps < TILE_N / 8; ++ps) tokens[ps] = key_token(p.f.prob, di.pt.kv, n * TILE_N + ps * 8 + rsub);
-        INTRA_TRACE_EV(lt == 0, 3, n, 4);
-        if (use > 0) {
-          ok = ptx::mbar_wait(&k_empty[stage], (use - 1) & 1, abort_p);
-          if (!ok) { if (*abort_p == 1) *abort_p = 22; break; }
-        }
-        INTRA_TRACE_EV(lt == 0, 3, n, 0);
-        const uint32_t kdst = k_smem0 + stage * TILE_BYTES;
-#pragma unroll
-        for (int ps = 0; ps < TILE_N / 8; ++ps) {
-          const int row = ps * 8 + rsub;
-          const int token = tokens[ps];
-          const void* src = token >= 0 ? static_cast<const void*>(kb + int64_t(token) * p.f.ks.ss) : static_cast<const void*>(p.f.k);
-          ptx::cp_async_16(kdst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
-        }
-        ptx::cp_async_mbar_arrive_noinc(&k_full[stage]);
-        INTRA_TRACE_EV(lt == 0, 3, n, 1);
-        if (use > 0) {
-          ok = ptx::mbar_wait(&v_empty[stage], (use - 1) & 1, abort_p);
-          if (!ok) { if (*abort_p == 1) *abort_p = 23; break; }
-        }
-        INTRA_TRACE_EV(lt == 0, 3, n, 2);
-        const uint32_t vdst = v_smem0 + stage * TILE_BYTES;
-#pragma unroll
-        for (int ps = 0; ps < TILE_N / 8; ++ps) {
-          const int row = ps * 8 + rsub;
-          const int token = tokens[ps];
-          const void* src = token >= 0 ? static_cast<const void*>(vb + int64_t(token) * p.f.vs.ss) : static_cast<const void*>(p.f.v);
-          ptx::cp_async_16(vdst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
-        }
-        ptx::cp_async_mbar_arrive_noinc(&v_full[stage]);
-        INTRA_TRACE_EV(lt == 0, 3, n, 3);
-      }
-      ++n_done;
+      ptx::cp_async_commit();
+      ptx::cp_async_wait<0>();
     }
-    ptx::cp_async_commit();
-    ptx::cp_async_wait<0>();
   } else {
     // ================================ MMA issue ==================================================
     ptx::setmaxnreg_dec<64>();
     if (warp == 12) {
       uint32_t kc = 0;                                    // key tiles issued so far
       uint32_t it0 = 0, it1 = 0;                          // PVs issued per sub-tile (p_full phases)
+      const uint64_t q0_desc = tile_desc_kmajor(q_smem0), q1_desc = tile_desc_kmajor(q_smem0 + TILE_BYTES);
+      const uint64_t k_desc0 = tile_desc_kmajor(k_smem0), v_desc0 = tile_desc_mnmajor(v_smem0);
+      constexpr uint64_t kStageStep = TILE_BYTES >> 4;    // descriptor distance between ring stages
       bool pend = false;                                  // PV1 of the previous key tile not yet issued
+      bool pend_last = false;                             // ... and it is the last one of its item
       uint32_t pend_acc = 0, pend_stage = 0;
       int n_done = 0;
       bool ok = true;
@@ -431,10 +436,10 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           ptx::fence_proxy_async_smem();
           ptx::tc_fence_after();
           INTRA_TRACE_EV(lane == 0, 0, n, 0);
-          const uint32_t k_smem = k_smem0 + stage * TILE_BYTES;
-          if (lane == 0) {
-            issue_qk(q_smem0, k_smem, tmem + 0);
-            ptx::mma_commit(&s_full[0]);
+          const uint64_t k_desc = k_desc0 + stage * kStageStep;
+          if (ptx::elect_one()) {
+            issue_qk_desc(q0_desc, k_desc, tmem + 0);
+            ptx::mma_commit(s0_full);
           }
           __syncwarp();
           if (pend) {
@@ -442,20 +447,17 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
             if (!ok) { if (*abort_p == 1) *abort_p = 33; break; }
             ptx::tc_fence_after();
             INTRA_TRACE_EV(lane == 0, 0, n, 1);
-            if (lane == 0) {
-              issue_pv(tmem + 128, v_smem0 + pend_stage * TILE_BYTES, tmem + 384, pend_acc != 0);
-              ptx::mma_commit(&o_done[1]);
-              ptx::mma_commit(&v_empty[pend_stage]);
+            if (ptx::elect_one()) {
+              issue_pv_desc(tmem + 128, v_desc0 + pend_stage * kStageStep, tmem + 384, pend_acc != 0);
+              if (pend_last) ptx::mma_commit(&o_done[1]);
             }
             __syncwarp();
             ++it1;
             pend = false;
           }
-          if (lane == 0) {
-            issue_qk(q_smem0 + TILE_BYTES, k_smem, tmem + 128);
-            ptx::mma_commit(&s_full[1]);
-            ptx::mma_commit(&k_empty[stage]);
-            if (n == n_kv - 1) ptx::mma_commit(q_empty);
+          if (ptx::elect_one()) {
+            issue_qk_desc(q1_desc, k_desc, tmem + 128);
+            ptx::mma_commit(&s1_full[kc & 1]);
           }
           __syncwarp();
           INTRA_TRACE_EV(lane == 0, 0, n, 2);
@@ -467,13 +469,15 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           if (!ok) { if (*abort_p == 1) *abort_p = 35; break; }
           ptx::tc_fence_after();
           INTRA_TRACE_EV(lane == 0, 0, n, 4);
-          if (lane == 0) {
-            issue_pv(tmem + 0, v_smem0 + stage * TILE_BYTES, tmem + 256, n > 0);
-            ptx::mma_commit(&o_done[0]);
+          if (ptx::elect_one()) {
+            issue_pv_desc(tmem + 0, v_desc0 + stage * kStageStep, tmem + 256, n > 0);
+            if (n == n_kv - 1) ptx::mma_commit(&o_done[0]);
           }
           __syncwarp();
+          INTRA_TRACE_EV(lane == 0, 0, n, 5);
           ++it0;
           pend = true;
+          pend_last = (n == n_kv - 1);
           pend_acc = n > 0 ? 1u : 0u;
           pend_stage = stage;
         }
@@ -484,22 +488,22 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
         if (!ok && *abort_p == 1) *abort_p = 36;
         if (ok) {
           ptx::tc_fence_after();
-          if (lane == 0) {
-            issue_pv(tmem + 128, v_smem0 + pend_stage * TILE_BYTES, tmem + 384, pend_acc != 0);
+          if (ptx::elect_one()) {
+            issue_pv_desc(tmem + 128, v_desc0 + pend_stage * kStageStep, tmem + 384, pend_acc != 0);
             ptx::mma_commit(&o_done[1]);
-            ptx::mma_commit(&v_empty[pend_stage]);
           }
           __syncwarp();
         }
       }
       if (!ok) {                                          // let MMAs in flight finish before TMEM is freed
-        if (lane == 0) ptx::mma_commit(drain);
+        if (ptx::elect_one()) ptx::mma_commit(drain);
         __syncwarp();
         int dummy = 0;
         ptx::mbar_wait(drain, 0, &dummy, 100);
       }
     }
   }
+#undef INTRA_WAIT_TILE_DONE
 
   // ---- teardown --------------------------------------------------------------------------------
   ptx::tc_fence_before();

@@ -1,0 +1,140 @@
+// Register-level pieces of the online softmax one thread runs over its query row: a 128-wide score
+// tile lives in 128 registers (read from tensor memory) and is turned into 64 registers of packed
+// bf16 probabilities.
+//
+// The work is arranged for a single warp per scheduler with nobody to hide its latencies behind:
+//   * row maximum: four independent chains of three-input max instead of one 127-deep chain;
+//   * scale-and-shift and the row sum use the packed two-lane fp32 instructions (fma/add.f32x2);
+//   * exponentials are split between the two pipes that can produce them: most go to the MUFU
+//     (ex2.approx, 16 results per clock per SM), a fixed share is computed on the FMA pipe with a
+//     floor / degree-3-polynomial / exponent-add evaluation of 2^x whose relative error (8.6e-5) is far
+//     below the bf16 rounding applied to P right after.
+// Replaces the reference's softmax.h:66-166 (exp2f with folded scale, quad-shuffle row reductions),
+// which has four threads per row; here a row is one thread, so there are no shuffles at all.
+#pragma once
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace intra {
+namespace sm {
+
+using f2 = unsigned long long;   // two packed fp32 lanes
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ f2 pack2(float lo, float hi) {
+  f2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
+  f2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f2 add2(f2 a, f2 b) {
+  f2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f2 add2_rm(f2 a, f2 b) {   // round towards minus infinity
+  f2 d;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f2 sub2(f2 a, f2 b) {
+  f2 d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// Maximum of 128 scores held in registers.
+__device__ __forceinline__ float row_max(const float (&s)[128]) {
+  float a0 = max3(s[0], s[1], s[2]), a1 = max3(s[3], s[4], s[5]);
+  float a2 = max3(s[6], s[7], s[8]), a3 = max3(s[9], s[10], s[11]);
+#pragma unroll
+  for (int c = 12; c + 7 < 128; c += 8) {
+    a0 = max3(a0, s[c], s[c + 1]);
+    a1 = max3(a1, s[c + 2], s[c + 3]);
+    a2 = max3(a2, s[c + 4], s[c + 5]);
+    a3 = max3(a3, s[c + 6], s[c + 7]);
+  }
+  a0 = max3(a0, s[124], s[125]);           // 12 + 14 * 8 = 124: four scores left
+  a1 = max3(a1, s[126], s[127]);
+  return max3(a0, a1, fmaxf(a2, a3));
+}
+
+// 2^x for both lanes on the FMA pipe, for x <= 127: floor(x) by a round-down add of 1.5 * 2^23, the
+// fraction f = x - floor(x) in [0, 1) through a cubic fitted to 2^f (max relative error 8.6e-5), and
+// floor(x) added straight into the exponent field. Inputs below -126 (masked scores are -inf) are
+// clamped, which yields 2^-126, i.e. zero for every purpose here.
+__device__ __forceinline__ f2 ex2_fma_pipe(f2 x) {
+  constexpr float kMagic = 12582912.f;
+  float x0, x1;
+  unpack2(x, x0, x1);
+  const f2 xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const f2 magic = pack2(kMagic, kMagic);
+  const f2 t = add2_rm(xc, magic);
+  const f2 fl = sub2(t, magic);
+  const f2 f = sub2(xc, fl);
+  f2 p = fma2(f, pack2(0.07706704f, 0.07706704f), pack2(0.22764499f, 0.22764499f));
+  p = fma2(p, f, pack2(0.69511676f, 0.69511676f));
+  p = fma2(p, f, pack2(1.f, 1.f));
+  float p0, p1, t0, t1;
+  unpack2(p, p0, p1);
+  unpack2(t, t0, t1);
+  const float r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  const float r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+  return pack2(r0, r1);
+}
+
+// Which of every 8 consecutive score pairs take the FMA-pipe exponential (bit i = pair i).
+#ifndef INTRA_EX2_FMA_MASK
+#define INTRA_EX2_FMA_MASK 0x94u   // pairs 2, 4, 7: three of eight
+#endif
+
+// p[c] = 2^(s[c] * scale_log2 - base) for 32 scores starting at s[first]; returns their 16 packed
+// bf16 pairs in pk and adds the fp32 values into the four packed partial sums.
+__device__ __forceinline__ void exp_chunk(const float (&s)[128], int first, float scale_log2, float base,
+                                          uint32_t (&pk)[16], f2 (&sum)[4]) {
+  const f2 scale2 = pack2(scale_log2, scale_log2);
+  const f2 nbase2 = pack2(-base, -base);
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    const f2 x = fma2(pack2(s[first + 2 * c], s[first + 2 * c + 1]), scale2, nbase2);
+    f2 p;
+    float p0, p1;
+    if ((INTRA_EX2_FMA_MASK >> (c & 7)) & 1u) {
+      p = ex2_fma_pipe(x);
+      unpack2(p, p0, p1);
+    } else {
+      float x0, x1;
+      unpack2(x, x0, x1);
+      p0 = ptx::ex2(x0);
+      p1 = ptx::ex2(x1);
+      p = pack2(p0, p1);
+    }
+    sum[c & 3] = add2(sum[c & 3], p);
+    pk[c] = ptx::pack_bf16(p0, p1);
+  }
+}
+
+__device__ __forceinline__ float sum4(const f2 (&sum)[4]) {
+  float a, b, c, d, e, f, g, h;
+  unpack2(sum[0], a, b);
+  unpack2(sum[1], c, d);
+  unpack2(sum[2], e, f);
+  unpack2(sum[3], g, h);
+  return ((a + b) + (c + d)) + ((e + f) + (g + h));
+}
+
+}  // namespace sm
+}  // namespace intra
