@@ -258,6 +258,11 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     desc, B, S, H, Hkv, calls = WORKLOADS[args.workload]
+    H_total = H
+    if args.shard_heads:
+        if Hkv % world:
+            raise SystemExit(f"{Hkv} KV heads cannot be split over {world} ranks")
+        H, Hkv = H // world, Hkv // world               # this rank's block of KV-head groups
     g = torch.Generator(device="cpu").manual_seed(1000 + rank)
     hq = torch.randn(B, S, H, HEAD_DIM, generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
     hk = torch.randn(B, S, Hkv, HEAD_DIM, generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
@@ -333,6 +338,7 @@ def run_ours(args):
     if rank == 0:
         peaks, peaks_kind = load_peaks()
         ms_per_step = total_ms / args.steps
+        # flops_step is per rank; all ranks together did world * flops_step in the slowest rank's time
         value = world * flops_step / (ms_per_step * 1e-3) / 1e12
         e2e_value = world * flops_step / (e2e_ms / e_steps * 1e-3) / 1e12
         achieved = flops_calls[dom] / (launch_ms[dom] * 1e-3) / 1e12
@@ -340,9 +346,12 @@ def run_ours(args):
         line = {
             "metric": "effective sparse attention throughput (4*d*H*attended pairs / time)",
             "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if args.shard_heads else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": desc, "per_rank": "each rank runs the whole workload on its own seeded batch",
+            "config": {"workload": desc,
+                       "per_rank": (f"KV-head groups sharded: {H}/{Hkv} of {H_total} query heads per rank"
+                                    if args.shard_heads else
+                                    "each rank runs the whole workload on its own seeded batch"),
                        "l2": "inputs+outputs per step (%d MB) exceed the 126 MB L2; no explicit flush" % (
                            (2 * q.numel() + k.numel() + v.numel()) * 2 // 2**20),
                        "calls": [{"pattern": f"{f}/{p}", **kw, "ms": launch_ms[i], "tflops": flops_calls[i] / launch_ms[i] / 1e9}
@@ -383,6 +392,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--shard-heads", action="store_true",
+                    help="strong scaling: split the workload's KV-head groups over the ranks instead of "
+                         "giving every rank the whole workload")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "ours" and args.gpus != world:
