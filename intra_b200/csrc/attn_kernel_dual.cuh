@@ -3,8 +3,9 @@
 // memory. While one sub-tile's softmax runs on the CUDA cores, the tensor core works on the
 // other's QK^T and PV, so the two pipes overlap inside one CTA:
 //
-//   warps 0-3    softmax / correction / epilogue of sub-tile 0   (TMEM: S0 cols 0-127,   O0 cols 256-383)
-//   warps 4-7    the same for sub-tile 1                         (TMEM: S1 cols 128-255, O1 cols 384-511)
+//   warps 0-7    softmax / correction / epilogue, alternating between the sub-tiles: warps 0-3 own score
+//                columns 0-63 and warps 4-7 columns 64-127 of every row of BOTH sub-tiles
+//                (TMEM: S0 cols 0-127, S1 cols 128-255, O0 cols 256-383, O1 cols 384-511)
 //   warps 8-11   loaders: index maps + cp.async row gathers of Q0, Q1 and a 2-stage ring each for K, V;
 //                completion is signalled by the copies themselves (cp.async.mbarrier.arrive), so the
 //                loaders never wait for data, only for free slots
@@ -96,10 +97,12 @@ __device__ __forceinline__ DualItem dual_decode(const DualParams& p, int item) {
 __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const __grid_constant__ DualParams p) {
   extern __shared__ uint8_t smem_raw[];
   // barriers: 0 q_full, 1-2 k_full, 3-4 v_full, 5 s0_full, 6-7 s1_full[stage], 8-9 p_full[s],
-  //           10-11 o_done[s], 12 drain
-  __shared__ uint64_t bars[13];
+  //           10-11 o_done[s], 12 drain, 13 xbar (softmax threads' exchange rendezvous)
+  __shared__ uint64_t bars[14];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
+  __shared__ float xch_max[2][2][TILE_M];      // [phase parity][column half][row]: partial row maxima
+  __shared__ float xch_sum[2][2][TILE_M];      // [sub-tile][column half][row]: partial row sums
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -118,6 +121,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
   uint64_t* p_full = &bars[8];
   uint64_t* o_done = &bars[10];     // last PV of an item, per sub-tile
   uint64_t* drain = &bars[12];
+  uint64_t* xbar = &bars[13];
 
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem0 = smem_base;                                 // Q sub-tile s at + s * TILE_BYTES
@@ -135,10 +139,11 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
     ptx::mbar_init(s0_full, 1);
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&s1_full[s], 1);
-      ptx::mbar_init(&p_full[s], 128);
+      ptx::mbar_init(&p_full[s], 256);
       ptx::mbar_init(&o_done[s], 1);
     }
     ptx::mbar_init(drain, 1);
+    ptx::mbar_init(xbar, 256);
     ptx::fence_mbar_init();
   }
   if (warp == 0) {
@@ -163,16 +168,17 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
 
   if (warp < 8) {
     // ================================ softmax / correction / epilogue ==========================
+    // All eight warps work on ONE sub-tile at a time, alternating between the two: thread (half, row)
+    // owns the 64 score columns `half` of query row `row` of both sub-tiles. Two warps per scheduler
+    // then hide each other's latencies while the tensor core works on the other sub-tile. The two
+    // halves of a row agree on the row maximum through shared memory and a 256-arrival mbarrier.
     ptx::setmaxnreg_inc<192>();
-    const int s_idx = warp >> 2;                          // which sub-tile
-    const int row = tid & 127;                            // TMEM lane == query row of the sub-tile
+    const int half = warp >> 2;                           // which 64 columns of every score tile
+    const int row = tid & 127;                            // TMEM lane == query row
     const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
-    const uint32_t s_addr = lane_addr + s_idx * 128;
-    const uint32_t o_addr = lane_addr + 256 + s_idx * 128;
-    uint64_t* my_p_full = &p_full[s_idx];
-    uint64_t* my_o_done = &o_done[s_idx];
     const float scale_log2 = p.f.scale_log2;
     uint32_t it = 0;                                      // key tiles processed so far by this CTA
+    uint32_t ph = 0;                                      // exchange phases so far (double-buffer index)
     uint32_t n_done = 0;                                  // items finished
     bool ok = true;
 
@@ -182,100 +188,134 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
       const DualItem di = dual_decode(p, item);
       const int n_kv = di.pt.kv.n_kv_tiles;
       if (n_kv == 0) continue;
-      int token, lo, hi;
-      pair_q_row(p.f.prob, di.pt, s_idx, row, &token, &lo, &hi);
-      float m_run = -CUDART_INF_F;
-      float l_run = 0.f;
+      int token[2], lo[2], hi[2];
+      pair_q_row(p.f.prob, di.pt, 0, row, &token[0], &lo[0], &hi[0]);
+      pair_q_row(p.f.prob, di.pt, 1, row, &token[1], &lo[1], &hi[1]);
+      float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};    // running maxima (identical in both halves)
+      float l_part[2] = {0.f, 0.f};                       // this half's share of the row sums
 
-      for (int n = 0; n < n_kv; ++n, ++it) {
-        if (s_idx == 0) ok = ptx::mbar_wait(s0_full, it & 1, abort_p);
-        else ok = ptx::mbar_wait(&s1_full[it & 1], (it >> 1) & 1, abort_p);
-        if (!ok) { if (*abort_p == 1) *abort_p = 11 + s_idx; break; }
-        ptx::tc_fence_after();
-        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 0);
-
-        float s[TILE_N];
+      for (int n = 0; n < n_kv && ok; ++n, ++it) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_addr + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
-        ptx::tmem_wait_ld();
-        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 1);
+        for (int sx = 0; sx < 2; ++sx) {
+          if (sx == 0) ok = ptx::mbar_wait(s0_full, it & 1, abort_p);
+          else ok = ptx::mbar_wait(&s1_full[it & 1], (it >> 1) & 1, abort_p);
+          if (!ok) { if (*abort_p == 1) *abort_p = 11 + sx; break; }
+          ptx::tc_fence_after();
+          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 0);
+          const uint32_t s_addr = lane_addr + sx * 128;
+          const uint32_t o_addr = lane_addr + 256 + sx * 128 + half * 64;
 
-        const int u0 = n * TILE_N;
-        if (lo > u0 || hi < u0 + TILE_N - 1) {            // this row's interval does not cover the tile
+          float s[64];
+          ptx::tmem_ld32(s_addr + half * 64, reinterpret_cast<uint32_t*>(s));
+          ptx::tmem_ld32(s_addr + half * 64 + 32, reinterpret_cast<uint32_t*>(s) + 32);
+          ptx::tmem_wait_ld();
+          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 1);
+
+          const int u0 = n * TILE_N + half * 64;
+          if (lo[sx] > u0 || hi[sx] < u0 + 63) {          // this row's interval does not cover these columns
 #pragma unroll
-          for (int c = 0; c < TILE_N; ++c) {
-            const int u = u0 + c;
-            if (u < lo || u > hi) s[c] = -CUDART_INF_F;
+            for (int c = 0; c < 64; ++c) {
+              const int u = u0 + c;
+              if (u < lo[sx] || u > hi[sx]) s[c] = -CUDART_INF_F;
+            }
           }
-        }
-        const float m_new = fmaxf(m_run, sm::row_max(s));
-        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 2);
-        // Move the running maximum only when the scores outgrow it by 2^8; until then p is merely
-        // scaled by a constant that the final division by the row sum removes.
-        const bool grow = (m_new - m_run) * scale_log2 > RESCALE_THRESHOLD;
-        float alpha = 1.f;
-        if (grow) {
-          alpha = ptx::ex2((m_run - m_new) * scale_log2);  // 0 when m_run is still -inf
-          l_run *= alpha;
-          m_run = m_new;
-        }
-        if (n > 0 && __any_sync(0xffffffffu, grow)) {     // rare once the maximum has settled
-          // The previous key tile's PV was issued before the QK^T whose completion was just waited
-          // for, and the tensor pipe completes in order: O is quiescent here.
+          const float my_max = sm::row_max(s);
+          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 5);
+          xch_max[ph & 1][half][row] = my_max;
+          ptx::mbar_arrive(xbar);                         // rendezvous of all 256 softmax threads (bounded,
+          ok = ptx::mbar_wait(xbar, ph & 1, abort_p);     // unlike bar.sync); also: everyone has read S
+          if (!ok) { if (*abort_p == 1) *abort_p = 17; break; }
+          const float tile_max = fmaxf(my_max, xch_max[ph & 1][half ^ 1][row]);
+          ++ph;
+          const float m_new = fmaxf(m_run[sx], tile_max);
+          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 2);
+          // Move the running maximum only when the scores outgrow it by 2^8; until then p is merely
+          // scaled by a constant that the final division by the row sum removes.
+          const bool grow = (m_new - m_run[sx]) * scale_log2 > RESCALE_THRESHOLD;
+          float alpha = 1.f;
+          if (grow) {
+            alpha = ptx::ex2((m_run[sx] - m_new) * scale_log2);    // 0 when the maximum is still -inf
+            l_part[sx] *= alpha;
+            m_run[sx] = m_new;
+          }
+          if (n > 0 && __any_sync(0xffffffffu, grow)) {   // rare once the maximum has settled
+            // The previous key tile's PV was issued before the QK^T whose completion was just waited
+            // for, and the tensor pipe completes in order: O is quiescent here.
 #pragma unroll 1
-          for (int c = 0; c < HEAD_DIM / 16; ++c) {
-            uint32_t o[16];
-            ptx::tmem_ld16(o_addr + c * 16, o);
-            ptx::tmem_wait_ld();
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[16];
+              ptx::tmem_ld16(o_addr + c * 16, o);
+              ptx::tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            ptx::tmem_st16(o_addr + c * 16, o);
+              for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              ptx::tmem_st16(o_addr + c * 16, o);
+            }
           }
-        }
-        const float base = (m_run == -CUDART_INF_F) ? 0.f : m_run * scale_log2;
-        sm::f2 sum[4] = {0ull, 0ull, 0ull, 0ull};
+          const float base = (m_run[sx] == -CUDART_INF_F) ? 0.f : m_run[sx] * scale_log2;
+          sm::f2 sum[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {                  // 32 scores -> 16 packed columns of P
-          uint32_t pk[16];
-          sm::exp_chunk(s, c4 * 32, scale_log2, base, pk, sum);
-          ptx::tmem_st16(s_addr + c4 * 16, pk);
+          for (int c2 = 0; c2 < 2; ++c2) {                // 32 scores -> 16 packed columns of P
+            uint32_t pk[16];
+            sm::exp_chunk(s, c2 * 32, scale_log2, base, pk, sum);
+            ptx::tmem_st16(s_addr + half * 32 + c2 * 16, pk);
+            INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 6 + c2);
+          }
+          l_part[sx] += sm::sum4(sum);
+          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 3);
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(&p_full[sx]);
+          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 4);
         }
-        l_run += sm::sum4(sum);
-        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 3);
-        ptx::tmem_wait_st();
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(my_p_full);
-        INTRA_TRACE_EV((tid & 127) == 0, 1 + s_idx, n, 4);
       }
       if (!ok) break;
 
-      ok = ptx::mbar_wait(my_o_done, n_done & 1, abort_p);         // last PV of this item
-      if (!ok) { if (*abort_p == 1) *abort_p = 15 + s_idx; break; }
-      ++n_done;
-      ptx::tc_fence_after();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      const int h = s_idx ? di.h1 : di.h0;
-      __nv_bfloat16* dst = p.f.o + di.b * p.f.os.sb + int64_t(token < 0 ? 0 : token) * p.f.os.ss + h * p.f.os.sh;
+      // ---- epilogue: total row sums across the two halves, then each half stores its 64 columns
+      xch_sum[0][half][row] = l_part[0];
+      xch_sum[1][half][row] = l_part[1];
+      ptx::mbar_arrive(xbar);
+      ok = ptx::mbar_wait(xbar, ph & 1, abort_p);
+      if (!ok) { if (*abort_p == 1) *abort_p = 18; break; }
+      ++ph;
+      const float l_tot[2] = {l_part[0] + xch_sum[0][half ^ 1][row], l_part[1] + xch_sum[1][half ^ 1][row]};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t o[32];
-        ptx::tmem_ld32(o_addr + c * 32, o);
-        ptx::tmem_wait_ld();
-        if (token >= 0) {
+      for (int sx = 0; sx < 2; ++sx) {
+        ok = ptx::mbar_wait(&o_done[sx], n_done & 1, abort_p);     // last PV of this item
+        if (!ok) { if (*abort_p == 1) *abort_p = 15 + sx; break; }
+        ptx::tc_fence_after();
+        const float inv = l_tot[sx] > 0.f ? 1.f / l_tot[sx] : 0.f;
+        const int h = sx ? di.h1 : di.h0;
+        const int tk = token[sx];
+        __nv_bfloat16* dst = p.f.o + di.b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh + half * 64;
+        const uint32_t o_addr = lane_addr + 256 + sx * 128 + half * 64;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = ptx::pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-            w.y = ptx::pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-            w.z = ptx::pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-            w.w = ptx::pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = w;
+        for (int c = 0; c < 2; ++c) {
+          uint32_t o[32];
+          ptx::tmem_ld32(o_addr + c * 32, o);
+          ptx::tmem_wait_ld();
+          if (tk >= 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 w;
+              w.x = ptx::pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+              w.y = ptx::pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+              w.z = ptx::pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+              w.w = ptx::pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = w;
+            }
           }
         }
       }
-      // The next item's first PV overwrites O only after this warp's next p_full arrive, which is
+      if (!ok) break;
+      ++n_done;
+      // The next item's first PV overwrites O only after this thread's next p_full arrive, which is
       // ordered after these loads; S is rewritten by the tensor core only after the last PV above.
+      // The barrier also keeps a fast thread's next exchange from overtaking a slow reader of xch_sum.
       ptx::tc_fence_before();
+      ptx::mbar_arrive(xbar);
+      ok = ptx::mbar_wait(xbar, ph & 1, abort_p);
+      if (!ok) { if (*abort_p == 1) *abort_p = 19; break; }
+      ++ph;
     }
   } else if (warp < 12) {
     // ================================ loaders ===================================================

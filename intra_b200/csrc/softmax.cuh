@@ -56,19 +56,22 @@ __device__ __forceinline__ f2 sub2(f2 a, f2 b) {
   return d;
 }
 
-// Maximum of 128 scores held in registers.
-__device__ __forceinline__ float row_max(const float (&s)[128]) {
+// Maximum of N scores held in registers (N = 64 or 128): four chains of three-input max.
+template <int N>
+__device__ __forceinline__ float row_max(const float (&s)[N]) {
+  static_assert(N % 8 == 4 || N % 8 == 0, "N must be a multiple of 4");
   float a0 = max3(s[0], s[1], s[2]), a1 = max3(s[3], s[4], s[5]);
   float a2 = max3(s[6], s[7], s[8]), a3 = max3(s[9], s[10], s[11]);
+  constexpr int kLoopEnd = 12 + ((N - 12) / 8) * 8;
 #pragma unroll
-  for (int c = 12; c + 7 < 128; c += 8) {
+  for (int c = 12; c < kLoopEnd; c += 8) {
     a0 = max3(a0, s[c], s[c + 1]);
     a1 = max3(a1, s[c + 2], s[c + 3]);
     a2 = max3(a2, s[c + 4], s[c + 5]);
     a3 = max3(a3, s[c + 6], s[c + 7]);
   }
-  a0 = max3(a0, s[124], s[125]);           // 12 + 14 * 8 = 124: four scores left
-  a1 = max3(a1, s[126], s[127]);
+  a0 = max3(a0, s[N - 4], s[N - 3]);        // N - 12 is 4 mod 8: four scores left
+  a1 = max3(a1, s[N - 2], s[N - 1]);
   return max3(a0, a1, fmaxf(a2, a3));
 }
 
@@ -103,7 +106,8 @@ __device__ __forceinline__ f2 ex2_fma_pipe(f2 x) {
 
 // p[c] = 2^(s[c] * scale_log2 - base) for 32 scores starting at s[first]; returns their 16 packed
 // bf16 pairs in pk and adds the fp32 values into the four packed partial sums.
-__device__ __forceinline__ void exp_chunk(const float (&s)[128], int first, float scale_log2, float base,
+template <int N>
+__device__ __forceinline__ void exp_chunk(const float (&s)[N], int first, float scale_log2, float base,
                                           uint32_t (&pk)[16], f2 (&sum)[4]) {
   const f2 scale2 = pack2(scale_log2, scale_log2);
   const f2 nbase2 = pack2(-base, -base);
