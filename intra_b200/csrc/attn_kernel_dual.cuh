@@ -6,9 +6,10 @@
 //   warps 0-7    softmax / correction / epilogue, alternating between the sub-tiles: warps 0-3 own score
 //                columns 0-63 and warps 4-7 columns 64-127 of every row of BOTH sub-tiles
 //                (TMEM: S0 cols 0-127, S1 cols 128-255, O0 cols 256-383, O1 cols 384-511)
-//   warps 8-11   loaders: index maps + cp.async row gathers of Q0, Q1 and a 2-stage ring each for K, V;
-//                completion is signalled by the copies themselves (cp.async.mbarrier.arrive), so the
-//                loaders never wait for data, only for free slots
+//   warps 8-11   when the tiles are TMA boxes: epilogue warps (O of a finished item -> bf16 -> global while
+//                the softmax warps are already on the next item); otherwise loaders: index maps +
+//                cp.async row gathers, completion signalled by the copies themselves
+//   warp 13      one thread issues the TMA loads of Q0, Q1 and a 2-stage ring each for K, V
 //   warp 12      one thread issues tcgen05.mma in the order QK0(n) PV1(n-1) QK1(n) PV0(n), carried on
 //                across tile boundaries so the next tile's first QK^T overlaps this tile's last softmax
 //
@@ -34,10 +35,14 @@ namespace intra {
 // trace[(role * 64 + (iteration & 63)) * 8 + event] = clock64().
 #ifdef INTRA_TRACE
 __device__ long long g_trace[4 * 64 * 8];
+__device__ long long g_trace_item[4 * 32 * 8];
 #define INTRA_TRACE_EV(cond, role, iter, ev) \
   do { if ((cond) && blockIdx.x == 0 && seq == 0 && (iter) < 64) g_trace[((role) * 64 + (iter)) * 8 + (ev)] = clock64(); } while (0)
+#define INTRA_TRACE_ITEM(cond, role, ev) \
+  do { if ((cond) && blockIdx.x == 0 && seq < 32) g_trace_item[((role) * 32 + seq) * 8 + (ev)] = clock64(); } while (0)
 #else
 #define INTRA_TRACE_EV(cond, role, iter, ev) do {} while (0)
+#define INTRA_TRACE_ITEM(cond, role, ev) do {} while (0)
 #endif
 
 constexpr int DUAL_THREADS = 512;
@@ -52,6 +57,7 @@ struct DualParams {
   int heads_per_item;   // row_pairs ? H : H / 2  (number of items per pair tile and batch)
   int n_items;          // n_pair_tiles * B * heads_per_item
   int use_tma;          // tiles are fetched as TMA boxes (tma_maps.h) instead of cp.async row gathers
+  int wide_stores;      // every output row is 32-byte aligned: 256-bit global stores
   TmaMaps maps;
 };
 
@@ -94,15 +100,43 @@ __device__ __forceinline__ DualItem dual_decode(const DualParams& p, int item) {
   return it;
 }
 
+// Normalise `ncols` (a multiple of 32) accumulator columns of this thread's TMEM lane by `inv` and store
+// them as bf16 to `dst` (this row's position in the output). `wide` selects 32-byte stores, which need
+// 32-byte aligned rows; tensor-memory loads are finished when the function returns.
+__device__ __forceinline__ void store_o_row(uint32_t o_addr, int ncols, float inv, __nv_bfloat16* dst, bool valid,
+                                            bool wide) {
+  for (int c = 0; c < ncols / 32; ++c) {
+    uint32_t o[32];
+    ptx::tmem_ld32(o_addr + c * 32, o);
+    ptx::tmem_wait_ld();
+    if (valid) {
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        w[i] = ptx::pack_bf16(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+      __nv_bfloat16* d = dst + c * 32;
+      if (wide) {
+        ptx::st_global_v8(d, w);
+        ptx::st_global_v8(d + 16, w + 8);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(d + i * 8) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const __grid_constant__ DualParams p) {
   extern __shared__ uint8_t smem_raw[];
   // barriers: 0 q_full, 1-2 k_full, 3-4 v_full, 5 s0_full, 6-7 s1_full[stage], 8-9 p_full[s],
-  //           10-11 o_done[s], 12 drain, 13 xbar (softmax threads' exchange rendezvous)
-  __shared__ uint64_t bars[14];
+  //           10-11 o_done[s], 12 drain, 13 xbar (softmax threads' exchange rendezvous),
+  //           14 l_ready (row sums of an item published), 15-16 o_free[s] (O of an item has been read)
+  __shared__ uint64_t bars[17];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
   __shared__ float xch_max[2][2][TILE_M];      // [phase parity][column half][row]: partial row maxima
-  __shared__ float xch_sum[2][2][TILE_M];      // [sub-tile][column half][row]: partial row sums
+  __shared__ float xch_sum[2][2][2][TILE_M];   // [item parity][sub-tile][column half][row]: partial row sums
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -122,6 +156,8 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
   uint64_t* o_done = &bars[10];     // last PV of an item, per sub-tile
   uint64_t* drain = &bars[12];
   uint64_t* xbar = &bars[13];
+  uint64_t* l_ready = &bars[14];
+  uint64_t* o_free = &bars[15];
 
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem0 = smem_base;                                 // Q sub-tile s at + s * TILE_BYTES
@@ -144,6 +180,9 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
     }
     ptx::mbar_init(drain, 1);
     ptx::mbar_init(xbar, 256);
+    ptx::mbar_init(l_ready, 8);
+    ptx::mbar_init(&o_free[0], p.use_tma ? 128 : 256);   // whoever runs the epilogue
+    ptx::mbar_init(&o_free[1], p.use_tma ? 128 : 256);
     ptx::fence_mbar_init();
   }
   if (warp == 0) {
@@ -191,6 +230,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
       int token[2], lo[2], hi[2];
       pair_q_row(p.f.prob, di.pt, 0, row, &token[0], &lo[0], &hi[0]);
       pair_q_row(p.f.prob, di.pt, 1, row, &token[1], &lo[1], &hi[1]);
+      INTRA_TRACE_ITEM(tid == 0, 1, 0);
       float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};    // running maxima (identical in both halves)
       float l_part[2] = {0.f, 0.f};                       // this half's share of the row sums
 
@@ -270,52 +310,40 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
       }
       if (!ok) break;
 
-      // ---- epilogue: total row sums across the two halves, then each half stores its 64 columns
-      xch_sum[0][half][row] = l_part[0];
-      xch_sum[1][half][row] = l_part[1];
+      // ---- row sums: publish this half's share; whoever stores O adds the two halves ----------
+      const int ipar = n_done & 1;
+      xch_sum[ipar][0][half][row] = l_part[0];
+      xch_sum[ipar][1][half][row] = l_part[1];
+      if (p.use_tma) {
+        // the epilogue warps take it from here; go straight on to the next item
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(l_ready);
+        ++n_done;
+        continue;
+      }
       ptx::mbar_arrive(xbar);
       ok = ptx::mbar_wait(xbar, ph & 1, abort_p);
       if (!ok) { if (*abort_p == 1) *abort_p = 18; break; }
       ++ph;
-      const float l_tot[2] = {l_part[0] + xch_sum[0][half ^ 1][row], l_part[1] + xch_sum[1][half ^ 1][row]};
 #pragma unroll
       for (int sx = 0; sx < 2; ++sx) {
+        INTRA_TRACE_ITEM(tid == 0, 1, 3 + 2 * sx);
         ok = ptx::mbar_wait(&o_done[sx], n_done & 1, abort_p);     // last PV of this item
         if (!ok) { if (*abort_p == 1) *abort_p = 15 + sx; break; }
         ptx::tc_fence_after();
-        const float inv = l_tot[sx] > 0.f ? 1.f / l_tot[sx] : 0.f;
+        INTRA_TRACE_ITEM(tid == 0, 1, 4 + 2 * sx);
+        const float l_tot = l_part[sx] + xch_sum[ipar][sx][half ^ 1][row];
+        const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
         const int h = sx ? di.h1 : di.h0;
         const int tk = token[sx];
         __nv_bfloat16* dst = p.f.o + di.b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh + half * 64;
-        const uint32_t o_addr = lane_addr + 256 + sx * 128 + half * 64;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t o[32];
-          ptx::tmem_ld32(o_addr + c * 32, o);
-          ptx::tmem_wait_ld();
-          if (tk >= 0) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 w;
-              w.x = ptx::pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-              w.y = ptx::pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-              w.z = ptx::pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-              w.w = ptx::pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = w;
-            }
-          }
-        }
+        store_o_row(lane_addr + 256 + sx * 128 + half * 64, 64, inv, dst, tk >= 0, p.wide_stores != 0);
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&o_free[sx]);
       }
       if (!ok) break;
       ++n_done;
-      // The next item's first PV overwrites O only after this thread's next p_full arrive, which is
-      // ordered after these loads; S is rewritten by the tensor core only after the last PV above.
-      // The barrier also keeps a fast thread's next exchange from overtaking a slow reader of xch_sum.
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(xbar);
-      ok = ptx::mbar_wait(xbar, ph & 1, abort_p);
-      if (!ok) { if (*abort_p == 1) *abort_p = 19; break; }
-      ++ph;
+      INTRA_TRACE_ITEM(tid == 0, 1, 2);
     }
   } else if (warp < 12) {
     // ================================ loaders ===================================================
@@ -326,54 +354,36 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
     int n_done = 0;
 
     if (p.use_tma) {
-      // ---- one thread drives the TMA unit; the other loader threads have nothing to do ----------
-      if (warp == 8 && lane == 0) {
-        ptx::prefetch_tensormap(&p.maps.q_main);
-        ptx::prefetch_tensormap(&p.maps.k_main);
-        ptx::prefetch_tensormap(&p.maps.v_main);
-        for (int seq = 0; ok; ++seq) {
-          const int item = dual_item_index(seq, cta, n_cta);
-          if (item >= p.n_items) break;
-          const DualItem di = dual_decode(p, item);
-          const int n_kv = di.pt.kv.n_kv_tiles;
-          if (n_kv == 0) continue;
-          if (n_done > 0) {                               // Q buffers: last QK^T of the previous item
-            INTRA_WAIT_TILE_DONE(kc - 1, 21);
-            if (!ok) break;
-          }
-          ptx::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
-          {
-            // an absent sub-tile (odd tile count) is fed the other one's rows; its results are dropped
-            const Tile& t0 = di.pt.sub[0].n_kv_tiles > 0 ? di.pt.sub[0] : di.pt.sub[1];
-            const Tile& t1 = di.pt.sub[1].n_kv_tiles > 0 ? di.pt.sub[1] : di.pt.sub[0];
-            int start; bool text;
-            tma_q_start(t0, &start, &text);
-            tma_fetch_tile(p.f.prob, t0, start, text, di.h0, di.b, &p.maps.q_main, &p.maps.q_text, q_smem0, q_full);
-            tma_q_start(t1, &start, &text);
-            tma_fetch_tile(p.f.prob, t1, start, text, di.h1, di.b, &p.maps.q_main, &p.maps.q_text,
-                           q_smem0 + TILE_BYTES, q_full);
-          }
-          for (int n = 0; n < n_kv && ok; ++n, ++kc) {
-            const int stage = kc % KV_STAGES;
-            int start; bool text;
-            tma_kv_start(di.pt.kv, n, &start, &text);
-            if (kc >= 2) {                                // K stage: QK1 of key tile kc-2
-              INTRA_WAIT_TILE_DONE(kc - 2, 22);
-              if (!ok) break;
-            }
-            ptx::mbar_arrive_expect_tx(&k_full[stage], TILE_BYTES);
-            tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.k_main, &p.maps.k_text,
-                           k_smem0 + stage * TILE_BYTES, &k_full[stage]);
-            if (kc >= 2) {                                // V stage: PV1 of key tile kc-2, issued before QK1 of kc-1
-              INTRA_WAIT_TILE_DONE(kc - 1, 23);
-              if (!ok) break;
-            }
-            ptx::mbar_arrive_expect_tx(&v_full[stage], TILE_BYTES);
-            tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.v_main, &p.maps.v_text,
-                           v_smem0 + stage * TILE_BYTES, &v_full[stage]);
-          }
-          ++n_done;
+      // ---- epilogue warps: O of a finished item -> global, while the softmax warps are already on
+      //      the next item. Thread = query row (all 128 columns). ------------------------------------
+      const int row = tid & 127;
+      const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
+      for (int seq = 0; ok; ++seq) {
+        const int item = dual_item_index(seq, cta, n_cta);
+        if (item >= p.n_items) break;
+        const DualItem di = dual_decode(p, item);
+        if (di.pt.kv.n_kv_tiles == 0) continue;
+        int token[2], lo, hi;
+        pair_q_row(p.f.prob, di.pt, 0, row, &token[0], &lo, &hi);
+        pair_q_row(p.f.prob, di.pt, 1, row, &token[1], &lo, &hi);
+        const int ipar = n_done & 1;
+        ok = ptx::mbar_wait(l_ready, ipar, abort_p);
+        if (!ok) { if (*abort_p == 1) *abort_p = 41; break; }
+#pragma unroll
+        for (int sx = 0; sx < 2; ++sx) {
+          ok = ptx::mbar_wait(&o_done[sx], ipar, abort_p);         // last PV of this item
+          if (!ok) { if (*abort_p == 1) *abort_p = 42 + sx; break; }
+          ptx::tc_fence_after();
+          const float l_tot = xch_sum[ipar][sx][0][row] + xch_sum[ipar][sx][1][row];
+          const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+          const int h = sx ? di.h1 : di.h0;
+          const int tk = token[sx];
+          __nv_bfloat16* dst = p.f.o + di.b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh;
+          store_o_row(lane_addr + 256 + sx * 128, 128, inv, dst, tk >= 0, p.wide_stores != 0);
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(&o_free[sx]);                           // the next item's first PV may overwrite O
         }
+        ++n_done;
       }
     } else {
       // ---- cp.async row gathers by all 128 loader threads (ragged shapes) ------------------------
@@ -448,6 +458,59 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
   } else {
     // ================================ MMA issue ==================================================
     ptx::setmaxnreg_dec<64>();
+    if (warp == 13 && p.use_tma && lane == 0) {
+      // ---- one thread drives the TMA unit ------------------------------------------------------------
+      uint32_t kc = 0;                                    // K / V tiles requested so far (ring position)
+      bool ok = true;
+      int n_done = 0;
+      ptx::prefetch_tensormap(&p.maps.q_main);
+      ptx::prefetch_tensormap(&p.maps.k_main);
+      ptx::prefetch_tensormap(&p.maps.v_main);
+      for (int seq = 0; ok; ++seq) {
+        const int item = dual_item_index(seq, cta, n_cta);
+        if (item >= p.n_items) break;
+        const DualItem di = dual_decode(p, item);
+        const int n_kv = di.pt.kv.n_kv_tiles;
+        if (n_kv == 0) continue;
+        if (n_done > 0) {                               // Q buffers: last QK^T of the previous item
+          INTRA_WAIT_TILE_DONE(kc - 1, 21);
+          if (!ok) break;
+        }
+        INTRA_TRACE_ITEM(true, 3, 0);
+        ptx::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+        {
+          // an absent sub-tile (odd tile count) is fed the other one's rows; its results are dropped
+          const Tile& t0 = di.pt.sub[0].n_kv_tiles > 0 ? di.pt.sub[0] : di.pt.sub[1];
+          const Tile& t1 = di.pt.sub[1].n_kv_tiles > 0 ? di.pt.sub[1] : di.pt.sub[0];
+          int start; bool text;
+          tma_q_start(t0, &start, &text);
+          tma_fetch_tile(p.f.prob, t0, start, text, di.h0, di.b, &p.maps.q_main, &p.maps.q_text, q_smem0, q_full);
+          tma_q_start(t1, &start, &text);
+          tma_fetch_tile(p.f.prob, t1, start, text, di.h1, di.b, &p.maps.q_main, &p.maps.q_text,
+                         q_smem0 + TILE_BYTES, q_full);
+        }
+        for (int n = 0; n < n_kv && ok; ++n, ++kc) {
+          const int stage = kc % KV_STAGES;
+          int start; bool text;
+          tma_kv_start(di.pt.kv, n, &start, &text);
+          if (kc >= 2) {                                // K stage: QK1 of key tile kc-2
+            INTRA_WAIT_TILE_DONE(kc - 2, 22);
+            if (!ok) break;
+          }
+          ptx::mbar_arrive_expect_tx(&k_full[stage], TILE_BYTES);
+          tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.k_main, &p.maps.k_text,
+                         k_smem0 + stage * TILE_BYTES, &k_full[stage]);
+          if (kc >= 2) {                                // V stage: PV1 of key tile kc-2, issued before QK1 of kc-1
+            INTRA_WAIT_TILE_DONE(kc - 1, 23);
+            if (!ok) break;
+          }
+          ptx::mbar_arrive_expect_tx(&v_full[stage], TILE_BYTES);
+          tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.v_main, &p.maps.v_text,
+                         v_smem0 + stage * TILE_BYTES, &v_full[stage]);
+        }
+        ++n_done;
+      }
+    }
     if (warp == 12) {
       uint32_t kc = 0;                                    // key tiles issued so far
       uint32_t it0 = 0, it1 = 0;                          // PVs issued per sub-tile (p_full phases)
@@ -457,6 +520,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
       bool pend = false;                                  // PV1 of the previous key tile not yet issued
       bool pend_last = false;                             // ... and it is the last one of its item
       uint32_t pend_acc = 0, pend_stage = 0;
+      int pend_item = 0;                                  // items finished before the pending PV1's item
       int n_done = 0;
       bool ok = true;
 
@@ -466,8 +530,10 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
         const DualItem di = dual_decode(p, item);
         const int n_kv = di.pt.kv.n_kv_tiles;
         if (n_kv == 0) continue;
+        INTRA_TRACE_ITEM(lane == 0, 0, 0);
         ok = ptx::mbar_wait(q_full, n_done & 1, abort_p);
         if (!ok) { if (*abort_p == 1) *abort_p = 31; break; }
+        INTRA_TRACE_ITEM(lane == 0, 0, 1);
         for (int n = 0; n < n_kv; ++n, ++kc) {
           const int stage = kc % KV_STAGES;
           const uint32_t par = (kc / KV_STAGES) & 1;
@@ -485,6 +551,10 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           if (pend) {
             ok = ptx::mbar_wait(&p_full[1], it1 & 1, abort_p);
             if (!ok) { if (*abort_p == 1) *abort_p = 33; break; }
+            if (pend_acc == 0 && pend_item > 0) {         // first PV1 of an item: O1 of the item before it
+              ok = ptx::mbar_wait(&o_free[1], (pend_item - 1) & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 38; break; }
+            }
             ptx::tc_fence_after();
             INTRA_TRACE_EV(lane == 0, 0, n, 1);
             if (ptx::elect_one()) {
@@ -507,6 +577,10 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           INTRA_TRACE_EV(lane == 0, 0, n, 3);
           ok = ptx::mbar_wait(&p_full[0], it0 & 1, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 35; break; }
+          if (n == 0 && n_done > 0) {                     // O0 of the previous item must have been read
+            ok = ptx::mbar_wait(&o_free[0], (n_done - 1) & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 37; break; }
+          }
           ptx::tc_fence_after();
           INTRA_TRACE_EV(lane == 0, 0, n, 4);
           if (ptx::elect_one()) {
@@ -520,12 +594,18 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           pend_last = (n == n_kv - 1);
           pend_acc = n > 0 ? 1u : 0u;
           pend_stage = stage;
+          pend_item = n_done;
         }
+        INTRA_TRACE_ITEM(lane == 0, 0, 2);
         ++n_done;
       }
       if (ok && pend) {
         ok = ptx::mbar_wait(&p_full[1], it1 & 1, abort_p);
         if (!ok && *abort_p == 1) *abort_p = 36;
+        if (ok && pend_acc == 0 && pend_item > 0) {
+          ok = ptx::mbar_wait(&o_free[1], (pend_item - 1) & 1, abort_p);
+          if (!ok && *abort_p == 1) *abort_p = 39;
+        }
         if (ok) {
           ptx::tc_fence_after();
           if (ptx::elect_one()) {

@@ -254,6 +254,7 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
     if (items <= 0 || items > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
     d.n_items = static_cast<int>(items);
     static const bool no_tma = [] { const char* v = std::getenv("INTRA_B200_NO_TMA"); return v && v[0] == '1'; }();
+    d.wide_stores = (reinterpret_cast<uintptr_t>(out) % 32 == 0 && os[0] % 16 == 0 && os[1] % 16 == 0 && os[2] % 16 == 0) ? 1 : 0;
     d.use_tma = !no_tma && tma_supported(p.prob) &&
                 build_maps(p.prob, p.q, p.qs, H, B, &d.maps.q_main, &d.maps.q_text) &&
                 build_maps(p.prob, p.k, p.ks, Hkv, B, &d.maps.k_main, &d.maps.k_text) &&
