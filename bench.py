@@ -39,8 +39,8 @@ if ROOT not in sys.path:
 HEAD_DIM = 128
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one Gather-1 launch of the default workload, from
-# the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = {"c2": None}
+# the ncu capture summarised under profiles/.
+NCU_TRAFFIC_BYTES = {"c2": 290626048 + 98915840}
 
 WORKLOADS = {
     # name: (description, B, S, H, Hkv, [(family, pattern, kwargs)])
@@ -362,7 +362,7 @@ def run_ours(args):
                     "ms_per_step": e2e_ms / e_steps},
             "gpu_launches": args.steps * len(calls),
             "clocks": clocks.summary(),
-            "roofline": {"bound": "tensor", "kernel": "intra_fwd_kernel (%s/%s launch)" % (calls[dom][0], calls[dom][1]),
+            "roofline": {"bound": "tensor", "kernel": "intra_fwd_dual_kernel (%s/%s launch)" % (calls[dom][0], calls[dom][1]),
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": peaks_kind + " bf16_tflops (burst)",
                          "frac_of_sustained": achieved / float(peaks.get("bf16_tflops_sustained", peak)),
