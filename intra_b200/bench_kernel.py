@@ -1,0 +1,145 @@
+"""Latency table in the format of the reference's kernel benchmark (benchmarks/bench_kernel.py).
+
+    python -m intra_b200.bench_kernel llm   [--seqlens 4096,...] [--groups 2,8] [--out file.json]
+    python -m intra_b200.bench_kernel image [--out file.json]
+
+Same flags, same protocol (CUDA events around each call, 10 warm-ups, median of 50) and the same row
+keys as the reference's benchmarks/results/*.json, so B200 rows can sit next to its A100 ones; each
+sparse entry additionally gets `<key>_tflops`, the effective sparse TFLOP/s (4*128*H*attended pairs).
+The dense baseline is torch SDPA with K/V expanded to the query heads, as in the reference.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import torch
+import torch.nn.functional as F
+
+from . import intra_image_attn, intra_llm_attn
+
+TEXT_LEN = 512
+
+
+def median_ms(fn, warmup, iters):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def dense_sdpa(q, k, v, causal):
+    rep = q.shape[2] // k.shape[2]
+    qt, kt, vt = (x.transpose(1, 2) for x in (q, k, v))
+    if rep > 1:
+        kt, vt = kt.repeat_interleave(rep, 1), vt.repeat_interleave(rep, 1)
+    return F.scaled_dot_product_attention(qt, kt, vt, is_causal=causal)
+
+
+def llm_pairs(pattern, S, G=8, W=576):
+    if pattern == "window":
+        return sum((min(64 * b + 64, S) - 64 * b) * (64 * b - max(64 * b - (W - 64), 0))
+                   + (min(64 * b + 64, S) - 64 * b) * (min(64 * b + 64, S) - 64 * b + 1) // 2
+                   for b in range((S + 63) // 64))
+    total = 0
+    for g in range(G):
+        if pattern == "scatter":
+            n = S // G + (1 if g < S % G else 0)
+        else:
+            n = (S // (G * G)) * G + min(max(S % (G * G) - g * G, 0), G)
+        total += n * (n + 1) // 2
+    return total
+
+
+def randn(*shape):
+    return torch.randn(*shape, device="cuda", dtype=torch.bfloat16)
+
+
+@torch.no_grad()
+def bench_llm(args):
+    rows = []
+    for S in args.seqlens:
+        q, k, v = randn(args.batch, S, args.heads, 128), randn(args.batch, S, args.kv_heads, 128), randn(args.batch, S, args.kv_heads, 128)
+        flop = lambda pairs: 4 * 128 * args.heads * args.batch * pairs
+        r = {"seqlen": S}
+        try:
+            r["dense"] = median_ms(lambda: dense_sdpa(q, k, v, True), args.warmup, args.iters)
+        except RuntimeError:
+            r["dense"] = None
+        for G in args.groups:
+            ms = median_ms(lambda: intra_llm_attn(q, k, v, "scatter", group_num=G), args.warmup, args.iters)
+            r[f"scatter_g{G}"] = ms
+            r[f"scatter_g{G}_tflops"] = flop(llm_pairs("scatter", S, G)) / ms / 1e9
+        if S % 64 == 0:
+            ms = median_ms(lambda: intra_llm_attn(q, k, v, "gather1", group_num=8), args.warmup, args.iters)
+            r["gather1_g8"] = ms
+            r["gather1_g8_tflops"] = flop(llm_pairs("gather1", S, 8)) / ms / 1e9
+        ms = median_ms(lambda: intra_llm_attn(q, k, v, "window", window=576), args.warmup, args.iters)
+        r["window576"] = ms
+        r["window576_tflops"] = flop(llm_pairs("window", S, W=576)) / ms / 1e9
+        if "scatter_g2" in r:
+            r["g2s4_32layer"] = 4 * r["scatter_g2"] + 28 * r["window576"]
+            if r["dense"] is not None:
+                r["dense_32layer"] = 32 * r["dense"]
+        rows.append(r)
+        print("  ".join(f"{a}={b:.3f}" if isinstance(b, float) else f"{a}={b}" for a, b in r.items()), flush=True)
+    return rows
+
+
+@torch.no_grad()
+def bench_image(args):
+    rows = []
+    for width in (64, 128):
+        S = TEXT_LEN + width * width
+        q, k, v = (randn(args.batch, S, args.image_heads, 128) for _ in range(3))
+        n_img = width * width // 8
+        pairs = {"scatter": S * (TEXT_LEN + n_img), "gather0": TEXT_LEN * (TEXT_LEN + n_img) + width * width * 768}
+        r = {"width": width, "seqlen": S}
+        try:
+            r["dense"] = median_ms(lambda: dense_sdpa(q, k, v, False), args.warmup, args.iters)
+        except RuntimeError:
+            r["dense"] = None
+        for pattern in ("scatter", "gather0"):
+            ms = median_ms(lambda: intra_image_attn(q, k, v, pattern, width), args.warmup, args.iters)
+            r[pattern] = ms
+            r[pattern + "_tflops"] = 4 * 128 * args.image_heads * args.batch * pairs[pattern] / ms / 1e9
+        r["interleaved_mean"] = (r["scatter"] + r["gather0"]) / 2
+        rows.append(r)
+        print("  ".join(f"{a}={b:.3f}" if isinstance(b, float) else f"{a}={b}" for a, b in r.items()), flush=True)
+    return rows
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("mode", choices=["llm", "image"])
+    p.add_argument("--seqlens", default="4096,8192,16384,32768,65536")
+    p.add_argument("--groups", default="2,8")
+    p.add_argument("--batch", type=int, default=1)
+    p.add_argument("--heads", type=int, default=32)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--image-heads", type=int, default=24)
+    p.add_argument("--warmup", type=int, default=10)
+    p.add_argument("--iters", type=int, default=50)
+    p.add_argument("--out", help="optional JSON output path")
+    args = p.parse_args()
+    args.seqlens = [int(x) for x in args.seqlens.split(",")]
+    args.groups = [int(x) for x in args.groups.split(",")]
+    print(f"device: {torch.cuda.get_device_name()}  torch {torch.__version__}")
+    rows = bench_llm(args) if args.mode == "llm" else bench_image(args)
+    if args.out:
+        with open(args.out, "w") as f:
+            json.dump({"device": torch.cuda.get_device_name(), "torch": torch.__version__,
+                       "args": {a: b for a, b in vars(args).items() if a != "out"}, "rows": rows}, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

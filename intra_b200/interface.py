@@ -62,7 +62,7 @@ def _empty_like(q):
     return out
 
 
-def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_scale=None):
+def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_scale=None, *, strict=True):
     """Causal prefill attention for language models.
 
     pattern="scatter": token i attends to earlier tokens j with j % group_num == i % group_num.
@@ -70,10 +70,11 @@ def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_
     pattern="window":  each 64-query block attends to itself and the preceding window - 64 tokens.
 
     Any seqlen works for scatter and window; gather1 keeps the reference's contract of
-    group_num=8 and seqlen % 64 == 0 (intra_attn/interface.py:41-42).
+    group_num=8 and seqlen % 64 == 0 (intra_attn/interface.py:41-42). `strict=False` (not in the
+    reference) lifts that restriction: the kernels handle Gather-1 for any group_num and seqlen.
     """
     q, k, v = _check(q, k, v)
-    if pattern == "gather1" and (group_num != 8 or q.shape[1] % (group_num * group_num)):
+    if strict and pattern == "gather1" and (group_num != 8 or q.shape[1] % (group_num * group_num)):
         raise ValueError(f"gather1 needs group_num=8 and seqlen % 64 == 0, got G={group_num}, S={q.shape[1]}")
     pid = LLM_PATTERNS[pattern]
     out = _empty_like(q)
@@ -87,7 +88,7 @@ def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_
     return out
 
 
-def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None):
+def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *, strict=True):
     """Bidirectional attention for FLUX-style sequences: 512 text tokens followed by a
     width x width grid of image tokens.
 
@@ -95,10 +96,13 @@ def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None):
                        64 tokens ride with groups 0..7; all text keys are always visible.
     pattern="gather0": each 8 x 8 image patch attends to a 16 x 16 window around it plus all text.
 
-    width must be 64 or 128 as in the reference (intra_attn/interface.py:60-63).
+    width must be 64 or 128 as in the reference (intra_attn/interface.py:60-63); `strict=False` (not in
+    the reference) accepts any width that is a multiple of 8 and at least 16.
     """
     q, k, v = _check(q, k, v)
-    if width not in (64, 128):
+    if not strict and (width < 16 or width % 8):
+        raise ValueError("width must be a multiple of 8 and at least 16")
+    if strict and width not in (64, 128):
         raise ValueError("image kernels are compiled for width 64 and 128")
     if q.shape[1] != TEXT_LEN + width * width:
         raise ValueError(f"expected {TEXT_LEN} text + {width}x{width} image tokens, got {q.shape[1]}")

@@ -201,3 +201,35 @@ def test_non_default_stream_and_scale(lib):
     st.synchronize()
     ref = _util.oracle_attention(q, k, v, oracle.llm_gather1_mask(1536, 8), scale=0.05, on_device=True)
     assert _util.max_abs_err(out, ref) <= _util.ATOL
+
+
+def test_flux_caller_and_relaxed_shapes(lib):
+    """The FLUX processor's call shape ((B, H, S, D) tensors, alternating patterns) and the shapes the
+    reference's wrapper refuses but the kernels handle (strict=False)."""
+    from intra_b200 import flux, intra_image_attn, intra_llm_attn
+    assert [flux.layer_pattern(i) for i in range(6)] == ["scatter", "scatter", "gather0", "gather0", "scatter", "scatter"]
+    assert flux.latent_width(512 + 64 * 64) == 64
+    with pytest.raises(ValueError):
+        flux.latent_width(512 + 60 * 60 + 1)
+    g = torch.Generator().manual_seed(4)
+    q, k, v = (torch.randn(1, 3, 512 + 64 * 64, 128, generator=g).to(torch.bfloat16).cuda() for _ in range(3))
+    with torch.no_grad():
+        for layer in (0, 2):
+            pattern = flux.layer_pattern(layer)
+            out = flux.flux_joint_attention(q, k, v, pattern)
+            assert out.shape == q.shape
+            mask = oracle.build_mask("image", pattern, q.shape[2], width=64)
+            ref = _util.oracle_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), mask, on_device=True)
+            assert _util.max_abs_err(out.transpose(1, 2), ref) <= _util.ATOL
+        # relaxed shapes through the Python API
+        ql, kl, vl = oracle.make_inputs(1, 1000, 4, 2, seed=8, device="cuda")
+        out = intra_llm_attn(ql, kl, vl, "gather1", group_num=5, strict=False)
+        ref = _util.oracle_attention(ql, kl, vl, oracle.llm_gather1_mask(1000, 5), on_device=True)
+        assert _util.max_abs_err(out, ref) <= _util.ATOL
+        qi, ki, vi = oracle.make_inputs(1, 512 + 48 * 48, 2, 2, seed=9, device="cuda")
+        for pattern in ("scatter", "gather0"):
+            out = intra_image_attn(qi, ki, vi, pattern, 48, strict=False)
+            ref = _util.oracle_attention(qi, ki, vi, oracle.build_mask("image", pattern, qi.shape[1], width=48), on_device=True)
+            assert _util.max_abs_err(out, ref) <= _util.ATOL
+        with pytest.raises(ValueError):
+            intra_image_attn(qi, ki, vi, "scatter", 48)
