@@ -79,8 +79,8 @@ int intra_b200_visited_host(int family, int pattern, int S, int param, uint8_t* 
 int intra_b200_visited_device(int family, int pattern, int S, int param, uint8_t* counts_dev,
                               int device, void* cuda_stream);
 /* Same as intra_b200_visited_host for the decomposition into pairs of row tiles that share their
- * key tiles (used when the query heads of a KV group cannot be paired); INTRA_ERR_UNSUPPORTED for
- * Gather-0, which has no such pairs. */
+ * key tiles (used when the query heads of a KV group cannot be paired) or, for Gather-0, pairs of
+ * equally long tiles that keep their own key lists. */
 int intra_b200_visited_pairs_host(int family, int pattern, int S, int param, uint8_t* counts);
 
 /* Test hook: number of tiles (CTAs per batch and head) and key tiles summed over them, i.e. the

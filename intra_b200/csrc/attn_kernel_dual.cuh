@@ -56,25 +56,74 @@ struct DualParams {
   int n_pair_tiles;     // pair tiles per (batch, head or head pair)
   int heads_per_item;   // row_pairs ? H : H / 2  (number of items per pair tile and batch)
   int n_items;          // n_pair_tiles * B * heads_per_item
+  int split_kv;         // the two sub-tiles keep their own key lists (Gather-0): K / V buffer s belongs to sub-tile s
   int use_tma;          // tiles are fetched as TMA boxes (tma_maps.h) instead of cp.async row gathers
   int wide_stores;      // every output row is 32-byte aligned: 256-bit global stores
   TmaMaps maps;
 };
 
+// The tensor maps of one operand (Q, K or V).
+struct TmaOperand {
+  const CUtensorMap* main_map;
+  const CUtensorMap* text_map;
+  const CUtensorMap* aux_map;
+};
+
 // Fetch the 128 rows starting at `start` of tile `t` into the swizzled tile at `dst` (two boxes, one
 // per half of the head dim), completion counted on `bar`.
 __device__ __forceinline__ void tma_fetch_tile(const Problem& prob, const Tile& t, int start, bool text, int head,
-                                               int batch, const CUtensorMap* main_map, const CUtensorMap* text_map,
-                                               uint32_t dst, uint64_t* bar) {
+                                               int batch, const TmaOperand& op, uint32_t dst, uint64_t* bar) {
   int c[5];
   const int is_text = tma_box_coords(prob, t, start, text, head, batch, c);
-  const bool rank4 = is_text || prob.kind == KIND_LLM_WINDOW;
-  const CUtensorMap* m = is_text ? text_map : main_map;
+  const bool rank4 = is_text || t.kind == KIND_LLM_WINDOW;
+  // a Gather-0 problem's text tiles are image-Scatter tiles whose image keys come through the aux view
+  const CUtensorMap* m = is_text ? op.text_map : (prob.kind == KIND_IMG_GATHER0 ? op.aux_map : op.main_map);
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     if (rank4) ptx::tma_load_4d(dst + half * HALF_BYTES, m, bar, half * 64, c[1], c[2], c[3]);
     else ptx::tma_load_5d(dst + half * HALF_BYTES, m, bar, half * 64, c[1], c[2], c[3], c[4]);
   }
+}
+
+// Query rows of sub-tile `t` (TILE_BYTES in all).
+__device__ __forceinline__ void tma_fetch_q(const Problem& prob, const Tile& t, int head, int batch, const TmaOperand& op,
+                                            uint32_t dst, uint64_t* bar) {
+  if (t.kind == KIND_IMG_GATHER0) {                       // two 8x8 patches, 64 rows each
+#pragma unroll
+    for (int patch = 0; patch < 2; ++patch) {
+      const int pc = t.pcol + (patch == 1 && t.nq > PATCH * PATCH ? 1 : 0);   // no right patch: the left one again
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+        ptx::tma_load_5d(dst + half * HALF_BYTES + patch * (64 * 128), op.main_map, bar, half * 64, PATCH * pc,
+                         PATCH * t.prow, head, batch);
+    }
+    return;
+  }
+  int start; bool text;
+  tma_q_start(t, &start, &text);
+  tma_fetch_tile(prob, t, start, text, head, batch, op, dst, bar);
+}
+
+// Key tile n of key-slot map `kv` (TILE_BYTES).
+__device__ __forceinline__ void tma_fetch_kv(const Problem& prob, const Tile& kv, int n, int head, int batch,
+                                             const TmaOperand& op, uint32_t dst, uint64_t* bar) {
+  if (kv.kind == KIND_IMG_GATHER0) {
+    // slots: 16 window columns (2 tiles) | 512 text (4 tiles) | the right patch's extra columns (1 tile)
+    if (n >= 2 && n < 6) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+        ptx::tma_load_4d(dst + half * HALF_BYTES, op.text_map, bar, half * 64, TILE_N * (n - 2), head, batch);
+    } else {
+      const int wc0 = n < 2 ? 8 * n : WIN + 8 * (n - 6);
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+        ptx::tma_load_5d(dst + half * HALF_BYTES, op.main_map, bar, half * 64, kv.r0, kv.c0 + wc0, head, batch);
+    }
+    return;
+  }
+  int start; bool text;
+  tma_kv_start(kv, n, &start, &text);
+  tma_fetch_tile(prob, kv, start, text, head, batch, op, dst, bar);
 }
 
 struct DualItem {
@@ -125,6 +174,116 @@ __device__ __forceinline__ void store_o_row(uint32_t o_addr, int ncols, float in
       }
     }
   }
+}
+
+// Position in this CTA's stream of key tiles: item number `seq` of the CTA, key tile `n` of that item.
+struct TileCursor {
+  int seq, n, n_kv;
+  bool valid;
+  DualItem di;
+};
+// Move to the first non-empty item at or after c.seq.
+__device__ __forceinline__ void cursor_seek(const DualParams& p, TileCursor& c, int cta, int n_cta) {
+  for (;; ++c.seq) {
+    const int item = dual_item_index(c.seq, cta, n_cta);
+    if (item >= p.n_items) { c.valid = false; return; }
+    c.di = dual_decode(p, item);
+    c.n_kv = c.di.pt.kv.n_kv_tiles;
+    if (c.n_kv > 0) { c.n = 0; c.valid = true; return; }
+  }
+}
+__device__ __forceinline__ void cursor_next(const DualParams& p, TileCursor& c, int cta, int n_cta) {
+  if (++c.n < c.n_kv) return;
+  ++c.seq;
+  cursor_seek(p, c, cta, n_cta);
+}
+
+// Shared-memory layout and barriers the loaders of the split-K/V mode need.
+struct SplitLoaderCtx {
+  uint32_t q_smem0, k_smem0, v_smem0;
+  uint64_t *q_full, *k_full, *v_full, *s0_full, *s1_full;
+  volatile int* abort_p;
+};
+
+// Loader of the split-K/V mode (Gather-0): sub-tile s has its own key list and its own single K and V
+// buffer, refilled as soon as the MMA that read it has completed. Event driven: when QK0 of key tile
+// j is done (which, the pipe being in order, also means PV0 of tile j-1 is done) V0(j) and K0(j+1)
+// are requested; likewise for sub-tile 1, whose event also frees the Q buffers at an item's end.
+// kTma: one thread issues TMA boxes; otherwise all 128 loader threads gather rows with cp.async.
+template <bool kTma>
+__device__ __forceinline__ void split_loader(const DualParams& p, const SplitLoaderCtx& cx, int cta, int n_cta, int lt) {
+  const int chunk = lt & 15, rsub = lt >> 4;
+  const TmaOperand q_op = {&p.maps.q_main, &p.maps.q_text, &p.maps.q_main};
+  const TmaOperand k_op = {&p.maps.k_main, &p.maps.k_text, &p.maps.k_aux};
+  const TmaOperand v_op = {&p.maps.v_main, &p.maps.v_text, &p.maps.v_aux};
+
+  auto fetch_q = [&](const DualItem& di) {
+    if (kTma) {
+      ptx::mbar_arrive_expect_tx(cx.q_full, 2 * TILE_BYTES);
+      const Tile& t0 = pair_kv_map(di.pt, 1, 0);
+      const Tile& t1 = pair_kv_map(di.pt, 1, 1);
+      tma_fetch_q(p.f.prob, t0, di.h0, di.b, q_op, cx.q_smem0, cx.q_full);
+      tma_fetch_q(p.f.prob, t1, di.h1, di.b, q_op, cx.q_smem0 + TILE_BYTES, cx.q_full);
+    } else {
+#pragma unroll 1
+      for (int sx = 0; sx < 2; ++sx) {
+        const __nv_bfloat16* qb = p.f.q + di.b * p.f.qs.sb + (sx ? di.h1 : di.h0) * p.f.qs.sh + chunk * 8;
+#pragma unroll 4
+        for (int ps = 0; ps < TILE_M / 8; ++ps) {
+          const int row = ps * 8 + rsub;
+          int token, lo, hi;
+          pair_q_row(p.f.prob, di.pt, sx, row, &token, &lo, &hi);
+          const void* src = token >= 0 ? static_cast<const void*>(qb + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
+          ptx::cp_async_16(cx.q_smem0 + sx * TILE_BYTES + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+        }
+      }
+      ptx::cp_async_mbar_arrive_noinc(cx.q_full);
+    }
+  };
+  auto fetch_kv = [&](bool is_v, int sx, const TileCursor& c) {
+    const Tile& map = pair_kv_map(c.di.pt, 1, sx);
+    const uint32_t dst = (is_v ? cx.v_smem0 : cx.k_smem0) + sx * TILE_BYTES;
+    uint64_t* bar = is_v ? &cx.v_full[sx] : &cx.k_full[sx];
+    if (kTma) {
+      ptx::mbar_arrive_expect_tx(bar, TILE_BYTES);
+      tma_fetch_kv(p.f.prob, map, c.n, c.di.hk, c.di.b, is_v ? v_op : k_op, dst, bar);
+    } else {
+      const __nv_bfloat16* base = is_v ? p.f.v + c.di.b * p.f.vs.sb + c.di.hk * p.f.vs.sh + chunk * 8
+                                       : p.f.k + c.di.b * p.f.ks.sb + c.di.hk * p.f.ks.sh + chunk * 8;
+      const int64_t ss = is_v ? p.f.vs.ss : p.f.ks.ss;
+#pragma unroll 4
+      for (int ps = 0; ps < TILE_N / 8; ++ps) {
+        const int row = ps * 8 + rsub;
+        const int token = key_token(p.f.prob, map, c.n * TILE_N + row);
+        const void* src = token >= 0 ? static_cast<const void*>(base + int64_t(token) * ss) : static_cast<const void*>(p.f.k);
+        ptx::cp_async_16(dst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
+      }
+      ptx::cp_async_mbar_arrive_noinc(bar);
+    }
+  };
+
+  TileCursor cur;
+  cur.seq = 0;
+  cursor_seek(p, cur, cta, n_cta);
+  if (!cur.valid) return;
+  fetch_q(cur.di);
+  fetch_kv(false, 0, cur);
+  fetch_kv(false, 1, cur);
+  for (uint32_t j = 0;; ++j) {                            // j: key tiles of this CTA so far
+    TileCursor nxt = cur;
+    cursor_next(p, nxt, cta, n_cta);
+    const bool new_item = nxt.valid && nxt.n == 0;
+    if (!ptx::mbar_wait(cx.s0_full, j & 1, cx.abort_p)) { if (*cx.abort_p == 1) *cx.abort_p = 24; break; }
+    fetch_kv(true, 0, cur);
+    if (nxt.valid) fetch_kv(false, 0, nxt);
+    if (!ptx::mbar_wait(&cx.s1_full[j & 1], (j >> 1) & 1, cx.abort_p)) { if (*cx.abort_p == 1) *cx.abort_p = 25; break; }
+    fetch_kv(true, 1, cur);
+    if (!nxt.valid) break;
+    if (new_item) fetch_q(nxt.di);
+    fetch_kv(false, 1, nxt);
+    cur = nxt;
+  }
+  if (!kTma) { ptx::cp_async_commit(); ptx::cp_async_wait<0>(); }
 }
 
 __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const __grid_constant__ DualParams p) {
@@ -385,6 +544,9 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
         }
         ++n_done;
       }
+    } else if (p.split_kv) {
+      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, k_full, v_full, s0_full, s1_full, abort_p};
+      split_loader<false>(p, cx, cta, n_cta, lt);
     } else {
       // ---- cp.async row gathers by all 128 loader threads (ragged shapes) ------------------------
       const int chunk = lt & 15;                          // 16-byte chunk of the 256-byte row
@@ -458,7 +620,10 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
   } else {
     // ================================ MMA issue ==================================================
     ptx::setmaxnreg_dec<64>();
-    if (warp == 13 && p.use_tma && lane == 0) {
+    if (warp == 13 && p.use_tma && lane == 0 && p.split_kv) {
+      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, k_full, v_full, s0_full, s1_full, abort_p};
+      split_loader<true>(p, cx, cta, n_cta, 0);
+    } else if (warp == 13 && p.use_tma && lane == 0) {
       // ---- one thread drives the TMA unit ------------------------------------------------------------
       uint32_t kc = 0;                                    // K / V tiles requested so far (ring position)
       bool ok = true;
@@ -466,6 +631,9 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
       ptx::prefetch_tensormap(&p.maps.q_main);
       ptx::prefetch_tensormap(&p.maps.k_main);
       ptx::prefetch_tensormap(&p.maps.v_main);
+      const TmaOperand q_op = {&p.maps.q_main, &p.maps.q_text, &p.maps.q_main};
+      const TmaOperand k_op = {&p.maps.k_main, &p.maps.k_text, &p.maps.k_aux};
+      const TmaOperand v_op = {&p.maps.v_main, &p.maps.v_text, &p.maps.v_aux};
       for (int seq = 0; ok; ++seq) {
         const int item = dual_item_index(seq, cta, n_cta);
         if (item >= p.n_items) break;
@@ -482,31 +650,23 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           // an absent sub-tile (odd tile count) is fed the other one's rows; its results are dropped
           const Tile& t0 = di.pt.sub[0].n_kv_tiles > 0 ? di.pt.sub[0] : di.pt.sub[1];
           const Tile& t1 = di.pt.sub[1].n_kv_tiles > 0 ? di.pt.sub[1] : di.pt.sub[0];
-          int start; bool text;
-          tma_q_start(t0, &start, &text);
-          tma_fetch_tile(p.f.prob, t0, start, text, di.h0, di.b, &p.maps.q_main, &p.maps.q_text, q_smem0, q_full);
-          tma_q_start(t1, &start, &text);
-          tma_fetch_tile(p.f.prob, t1, start, text, di.h1, di.b, &p.maps.q_main, &p.maps.q_text,
-                         q_smem0 + TILE_BYTES, q_full);
+          tma_fetch_q(p.f.prob, t0, di.h0, di.b, q_op, q_smem0, q_full);
+          tma_fetch_q(p.f.prob, t1, di.h1, di.b, q_op, q_smem0 + TILE_BYTES, q_full);
         }
         for (int n = 0; n < n_kv && ok; ++n, ++kc) {
           const int stage = kc % KV_STAGES;
-          int start; bool text;
-          tma_kv_start(di.pt.kv, n, &start, &text);
           if (kc >= 2) {                                // K stage: QK1 of key tile kc-2
             INTRA_WAIT_TILE_DONE(kc - 2, 22);
             if (!ok) break;
           }
           ptx::mbar_arrive_expect_tx(&k_full[stage], TILE_BYTES);
-          tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.k_main, &p.maps.k_text,
-                         k_smem0 + stage * TILE_BYTES, &k_full[stage]);
+          tma_fetch_kv(p.f.prob, di.pt.kv, n, di.hk, di.b, k_op, k_smem0 + stage * TILE_BYTES, &k_full[stage]);
           if (kc >= 2) {                                // V stage: PV1 of key tile kc-2, issued before QK1 of kc-1
             INTRA_WAIT_TILE_DONE(kc - 1, 23);
             if (!ok) break;
           }
           ptx::mbar_arrive_expect_tx(&v_full[stage], TILE_BYTES);
-          tma_fetch_tile(p.f.prob, di.pt.kv, start, text, di.hk, di.b, &p.maps.v_main, &p.maps.v_text,
-                         v_smem0 + stage * TILE_BYTES, &v_full[stage]);
+          tma_fetch_kv(p.f.prob, di.pt.kv, n, di.hk, di.b, v_op, v_smem0 + stage * TILE_BYTES, &v_full[stage]);
         }
         ++n_done;
       }
@@ -535,8 +695,9 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
         if (!ok) { if (*abort_p == 1) *abort_p = 31; break; }
         INTRA_TRACE_ITEM(lane == 0, 0, 1);
         for (int n = 0; n < n_kv; ++n, ++kc) {
-          const int stage = kc % KV_STAGES;
-          const uint32_t par = (kc / KV_STAGES) & 1;
+          // shared keys: both sub-tiles read ring stage kc % 2; split keys: sub-tile s reads buffer s
+          const int stage = p.split_kv ? 0 : kc % KV_STAGES;
+          const uint32_t par = p.split_kv ? (kc & 1) : (kc / KV_STAGES) & 1;
           ok = ptx::mbar_wait(&k_full[stage], par, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 32; break; }
           ptx::fence_proxy_async_smem();
@@ -555,6 +716,11 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
               ok = ptx::mbar_wait(&o_free[1], (pend_item - 1) & 1, abort_p);
               if (!ok) { if (*abort_p == 1) *abort_p = 38; break; }
             }
+            if (p.split_kv) {                             // sub-tile 1's own V buffer
+              ok = ptx::mbar_wait(&v_full[1], (kc - 1) & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 40; break; }
+              ptx::fence_proxy_async_smem();
+            }
             ptx::tc_fence_after();
             INTRA_TRACE_EV(lane == 0, 0, n, 1);
             if (ptx::elect_one()) {
@@ -565,8 +731,14 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
             ++it1;
             pend = false;
           }
+          if (p.split_kv) {                               // sub-tile 1's own K buffer
+            ok = ptx::mbar_wait(&k_full[1], par, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 41; break; }
+            ptx::fence_proxy_async_smem();
+            ptx::tc_fence_after();
+          }
           if (ptx::elect_one()) {
-            issue_qk_desc(q1_desc, k_desc, tmem + 128);
+            issue_qk_desc(q1_desc, p.split_kv ? k_desc0 + kStageStep : k_desc, tmem + 128);
             ptx::mma_commit(&s1_full[kc & 1]);
           }
           __syncwarp();
@@ -593,7 +765,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           pend = true;
           pend_last = (n == n_kv - 1);
           pend_acc = n > 0 ? 1u : 0u;
-          pend_stage = stage;
+          pend_stage = p.split_kv ? 1 : stage;
           pend_item = n_done;
         }
         INTRA_TRACE_ITEM(lane == 0, 0, 2);
@@ -605,6 +777,11 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
         if (ok && pend_acc == 0 && pend_item > 0) {
           ok = ptx::mbar_wait(&o_free[1], (pend_item - 1) & 1, abort_p);
           if (!ok && *abort_p == 1) *abort_p = 39;
+        }
+        if (ok && p.split_kv) {
+          ok = ptx::mbar_wait(&v_full[1], (kc - 1) & 1, abort_p);
+          if (!ok && *abort_p == 1) *abort_p = 40;
+          ptx::fence_proxy_async_smem();
         }
         if (ok) {
           ptx::tc_fence_after();

@@ -134,8 +134,8 @@ bool encode_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* di
 }
 
 // The views of tma_maps.h for one (batch, token, head, 128) tensor with `heads` heads.
-bool build_maps(const Problem& p, const __nv_bfloat16* ptr, const TensorView& tv, int heads, int B, CUtensorMap* main_map,
-                CUtensorMap* text_map) {
+bool build_maps(const Problem& p, const __nv_bfloat16* ptr, const TensorView& tv, int heads, int B, bool is_query,
+                CUtensorMap* main_map, CUtensorMap* text_map, CUtensorMap* aux_map) {
   const cuuint64_t ss = cuuint64_t(tv.ss) * 2, sh = cuuint64_t(tv.sh) * 2, sb = cuuint64_t(tv.sb) * 2;
   if (tv.ss <= 0 || tv.sh <= 0 || tv.sb <= 0) return false;
   const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
@@ -165,6 +165,29 @@ bool build_maps(const Problem& p, const __nv_bfloat16* ptr, const TensorView& tv
       const cuuint32_t box[5] = {64, cuuint32_t(p.W), cuuint32_t(2 * (TILE_M / (p.W / 4))), 1, 1};
       const cuuint32_t estr[5] = {1, 4, 2, 1, 1};
       if (!encode_map(main_map, ptr + int64_t(TEXT_LEN) * tv.ss, 5, dims, str, box, estr)) return false;
+      const cuuint64_t tdims[4] = {128, TEXT_LEN, cuuint64_t(heads), cuuint64_t(B)};
+      const cuuint64_t tstr[3] = {ss, sh, sb};
+      const cuuint32_t tbox[4] = {64, 128, 1, 1};
+      return encode_map(text_map, ptr, 4, tdims, tstr, tbox, ones);
+    }
+    case KIND_IMG_GATHER0: {
+      // patch-pair tiles: keys as 16-row x 8-column boxes (row index fastest), queries as 8x8 patches
+      const __nv_bfloat16* img = ptr + int64_t(TEXT_LEN) * tv.ss;
+      const cuuint64_t dims[5] = {128, cuuint64_t(p.W), cuuint64_t(p.W), cuuint64_t(heads), cuuint64_t(B)};
+      if (is_query) {
+        const cuuint64_t str[4] = {ss, ss * p.W, sh, sb};            // (d, c, r, head, batch)
+        const cuuint32_t box[5] = {64, PATCH, PATCH, 1, 1};
+        if (!encode_map(main_map, img, 5, dims, str, box, ones)) return false;
+      } else {
+        const cuuint64_t str[4] = {ss * p.W, ss, sh, sb};            // (d, r, c, head, batch)
+        const cuuint32_t box[5] = {64, WIN, 8, 1, 1};
+        if (!encode_map(main_map, img, 5, dims, str, box, ones)) return false;
+        // text tiles: image-Scatter view of the keys
+        const cuuint64_t astr[4] = {ss, ss * p.W, sh, sb};
+        const cuuint32_t abox[5] = {64, cuuint32_t(p.W), cuuint32_t(2 * (TILE_M / (p.W / 4))), 1, 1};
+        const cuuint32_t aestr[5] = {1, 4, 2, 1, 1};
+        if (!encode_map(aux_map, img, 5, dims, astr, abox, aestr)) return false;
+      }
       const cuuint64_t tdims[4] = {128, TEXT_LEN, cuuint64_t(heads), cuuint64_t(B)};
       const cuuint64_t tstr[3] = {ss, sh, sb};
       const cuuint32_t tbox[4] = {64, 128, 1, 1};
@@ -241,13 +264,14 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
   p.B = B; p.H = H; p.Hkv = Hkv;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = g_dev[device].status_word;
-  // Patterns whose tiles pair up run on the persistent two-sub-tile kernel; Gather-0, whose tiles share
-  // no keys, on the one-tile kernel (INTRA_B200_SINGLE_TILE=1 forces the latter everywhere, for A/B runs).
+  // Everything runs on the persistent two-sub-tile kernel (Gather-0, whose tiles share no keys, with one
+  // K / V buffer per sub-tile); INTRA_B200_SINGLE_TILE=1 forces the one-tile kernel, for A/B runs.
   static const bool force_single = [] { const char* v = std::getenv("INTRA_B200_SINGLE_TILE"); return v && v[0] == '1'; }();
-  if (p.prob.kind != KIND_IMG_GATHER0 && !force_single) {
+  if (!force_single) {
     DualParams d;
     d.f = p;
-    d.row_pairs = ((H / Hkv) % 2 == 0) ? 0 : 1;
+    d.split_kv = p.prob.kind == KIND_IMG_GATHER0 ? 1 : 0;
+    d.row_pairs = (d.split_kv || (H / Hkv) % 2 != 0) ? 1 : 0;
     d.n_pair_tiles = n_pair_tiles(p.prob, d.row_pairs);
     d.heads_per_item = d.row_pairs ? H : H / 2;
     const int64_t items = int64_t(d.n_pair_tiles) * B * d.heads_per_item;
@@ -256,9 +280,9 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
     static const bool no_tma = [] { const char* v = std::getenv("INTRA_B200_NO_TMA"); return v && v[0] == '1'; }();
     d.wide_stores = (reinterpret_cast<uintptr_t>(out) % 32 == 0 && os[0] % 16 == 0 && os[1] % 16 == 0 && os[2] % 16 == 0) ? 1 : 0;
     d.use_tma = !no_tma && tma_supported(p.prob) &&
-                build_maps(p.prob, p.q, p.qs, H, B, &d.maps.q_main, &d.maps.q_text) &&
-                build_maps(p.prob, p.k, p.ks, Hkv, B, &d.maps.k_main, &d.maps.k_text) &&
-                build_maps(p.prob, p.v, p.vs, Hkv, B, &d.maps.v_main, &d.maps.v_text);
+                build_maps(p.prob, p.q, p.qs, H, B, true, &d.maps.q_main, &d.maps.q_text, &d.maps.k_aux) &&
+                build_maps(p.prob, p.k, p.ks, Hkv, B, false, &d.maps.k_main, &d.maps.k_text, &d.maps.k_aux) &&
+                build_maps(p.prob, p.v, p.vs, Hkv, B, false, &d.maps.v_main, &d.maps.v_text, &d.maps.v_aux);
     const int grid = static_cast<int>(items < g_dev[device].sm_count ? items : g_dev[device].sm_count);
     intra_fwd_dual_kernel<<<grid, DUAL_THREADS, DUAL_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(d);
   } else {
@@ -352,14 +376,16 @@ int intra_b200_visited_pairs_host(int family, int pattern, int S, int param, uin
   if (n <= 0) return INTRA_ERR_UNSUPPORTED;
   for (int idx = 0; idx < n; ++idx) {
     const PairTile pt = make_pair(prob, 1, idx);
+    const int split = prob.kind == KIND_IMG_GATHER0;
     for (int s = 0; s < 2; ++s) {
+      const Tile& kvmap = pair_kv_map(pt, split, s);
       for (int r = 0; r < TILE_M; ++r) {
         int token, lo, hi;
         pair_q_row(prob, pt, s, r, &token, &lo, &hi);
         if (token < 0) continue;
         if (token >= S || lo < 0 || hi >= pt.kv.n_kv_tiles * TILE_N) return INTRA_ERR_KERNEL;
         for (int u = lo; u <= hi; ++u) {
-          const int kt = key_token(prob, pt.kv, u);
+          const int kt = key_token(prob, kvmap, u);
           if (kt < 0) continue;
           if (kt >= S) return INTRA_ERR_KERNEL;
           uint8_t* c = counts + size_t(token) * S + kt;

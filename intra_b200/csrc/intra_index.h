@@ -282,7 +282,8 @@ INTRA_HD int key_token(const Problem& p, const Tile& t, int u) {
 //       coincide or nest: consecutive tiles of a Scatter / Gather-1 group, of the window sequence,
 //       or of an image-Scatter group. The shared key list is the union; each sub-tile's [lo, hi]
 //       is shifted into the union's slot numbering (only the window pattern needs a shift).
-//       Gather-0 has no two tiles with nested keys and is not paired.
+//       Gather-0 has no two tiles with nested keys: its pairs are two tiles with the same number of
+//       key tiles, each keeping its own key list (sub[s] is then also sub-tile s's key-slot map).
 struct PairTile {
   Tile sub[2];     // sub-tile with n_kv_tiles == 0 is absent (all its rows are padding)
   Tile kv;         // key-slot map of the pair; kv.n_kv_tiles key tiles are processed
@@ -296,6 +297,7 @@ INTRA_HD int n_pair_tiles(const Problem& p, int row_pairs) {
     case KIND_LLM_GATHER1: return ceil_div(p.tiles_m, 2) * p.G;
     case KIND_LLM_WINDOW: return ceil_div(p.n_tiles, 2);
     case KIND_IMG_SCATTER: return ceil_div(p.tiles_m, 2) * IMG_GROUPS;
+    case KIND_IMG_GATHER0: return IMG_GROUPS / 2 + ceil_div(p.n_tiles - IMG_GROUPS, 2);
     default: return 0;
   }
 }
@@ -327,6 +329,21 @@ INTRA_HD PairTile make_pair(const Problem& p, int row_pairs, int idx) {
       if (2 * mp + 1 < p.tiles_m) idx_second = (2 * mp + 1) * IMG_GROUPS + g;
       break;
     }
+    case KIND_IMG_GATHER0: {
+      // Gather-0 tiles share no keys: a "pair" is two tiles of equal length (two text chunks, or two
+      // patch pairs) that keep their own key lists; the caller gives each its own K / V buffers. A
+      // last tile without a partner is doubled.
+      PairTile sp;
+      sp.shift[0] = sp.shift[1] = 0;
+      const int first = idx < IMG_GROUPS / 2 ? 2 * idx : IMG_GROUPS + 2 * (idx - IMG_GROUPS / 2);
+      sp.sub[0] = make_tile(p, first);
+      sp.sub[1] = make_tile(p, first + 1 < p.n_tiles ? first + 1 : first);
+      if (first + 1 >= p.n_tiles) { sp.sub[1].n_kv_tiles = 0; sp.sub[1].nq = 0; }   // absent
+      sp.kv = sp.sub[0];                                   // only its n_kv_tiles is used in this mode:
+      sp.kv.n_kv_tiles = imax(sp.sub[0].n_kv_tiles, sp.sub[1].n_kv_tiles);   // shorter list is padded
+      sp.kv.nk = sp.kv.n_kv_tiles * TILE_N;
+      return sp;
+    }
     default: break;
   }
   Tile none = make_tile(p, 0);
@@ -343,6 +360,13 @@ INTRA_HD PairTile make_pair(const Problem& p, int row_pairs, int idx) {
   }
   if (!has0 && !has1) pt.kv.n_kv_tiles = 0;
   return pt;
+}
+
+// Key-slot map of sub-tile s: the pair's shared map, or the sub-tile's own when the pair does not share
+// keys (an absent sub-tile borrows the other one's so that loads stay in bounds).
+INTRA_HD const Tile& pair_kv_map(const PairTile& pt, int split_kv, int s) {
+  if (!split_kv) return pt.kv;
+  return pt.sub[s].n_kv_tiles > 0 ? pt.sub[s] : pt.sub[s ^ 1];
 }
 
 // q_row of sub-tile s of a pair, with lo / hi in the pair's slot numbering.

@@ -9,8 +9,11 @@
 //   image Scatter, image part    dims (d, c, r, head, batch), traversal strides (1, 4, 2), base at token 512
 //                                box (64, W, 2*128/(W/4)): every 4th column from c = b, every 2nd row from r = a
 //                text part       dims (d, token, head, batch), 512 tokens, box (64, 128)
+//   Gather-0 patch pairs  keys   dims (d, r, c, head, batch), box (64, 16, 8): 8 window columns, 16 rows each
+//                        queries dims (d, c, r, head, batch), box (64, 8, 8): one 8x8 patch, two boxes per tile
+//            text chunks         as image Scatter (the "aux" map) + the text map
 //
-// Shapes outside these conditions (ragged groups, odd widths) and Gather-0 use the cp.async gathers.
+// Shapes outside these conditions (ragged groups, odd widths) use the cp.async gathers.
 // This replaces the per-thread address arithmetic of the reference's loaders
 // (csrc/flash_attn/src/gmem_tile.h:481-1426, csrc/flash_attn/src/intra_copy.h:13-101).
 #pragma once
@@ -23,6 +26,7 @@ namespace intra {
 struct alignas(64) TmaMaps {
   CUtensorMap q_main, k_main, v_main;   // the pattern's strided view
   CUtensorMap q_text, k_text, v_text;   // image kinds: the 512 text tokens
+  CUtensorMap k_aux, v_aux;             // Gather-0: image-Scatter view for the keys of its text tiles
 };
 
 // Can the problem's tiles be fetched as TMA boxes?
@@ -31,7 +35,9 @@ INTRA_HD bool tma_supported(const Problem& p) {
     case KIND_LLM_SCATTER: return p.S % p.G == 0;
     case KIND_LLM_GATHER1: return p.S % (p.G * p.G) == 0 && TILE_M % p.G == 0 && p.G * p.G <= 65536;
     case KIND_LLM_WINDOW: return true;
-    case KIND_IMG_SCATTER: return p.W % 4 == 0 && p.W <= 256 && TILE_M % (p.W / 4) == 0 && 2 * (TILE_M / (p.W / 4)) <= 256;
+    case KIND_IMG_SCATTER:
+    case KIND_IMG_GATHER0:
+      return p.W % 8 == 0 && p.W <= 256 && TILE_M % (p.W / 4) == 0 && 2 * (TILE_M / (p.W / 4)) <= 256;
     default: return false;
   }
 }
@@ -41,7 +47,7 @@ INTRA_HD bool tma_supported(const Problem& p) {
 // Scatter image rows, token id for the window and for text rows. Returns 1 if the text map is meant.
 INTRA_HD int tma_box_coords(const Problem& p, const Tile& t, int start, bool text, int head, int batch, int c[5]) {
   c[0] = 0; c[1] = 0; c[2] = 0; c[3] = 0; c[4] = 0;
-  switch (p.kind) {
+  switch (t.kind) {
     case KIND_LLM_SCATTER:
       c[1] = t.g; c[2] = start; c[3] = head; c[4] = batch;
       return 0;

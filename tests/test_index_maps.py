@@ -50,9 +50,10 @@ def test_unsupported_shapes_are_rejected(lib):
     assert lib.intra_b200_visited_host(0, 0, 4, 8, buf.ctypes.data) == -2        # more groups than tokens
 
 
-@pytest.mark.parametrize("case", [c for c in MASK_CASES if c["pattern"] != "gather0"], ids=_util.case_id)
+@pytest.mark.parametrize("case", MASK_CASES, ids=_util.case_id)
 def test_row_pair_visited_set_equals_mask(lib, case):
-    """The decomposition into pairs of row tiles sharing their key tiles visits the same set."""
+    """The decomposition into pairs of row tiles (sharing their key tiles, or for Gather-0 keeping
+    their own) visits the same set."""
     S = case["S"]
     counts = np.zeros((S, S), dtype=np.uint8)
     rc = lib.intra_b200_visited_pairs_host(_util.FAMILY[case["family"]],
