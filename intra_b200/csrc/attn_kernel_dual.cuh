@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
       ptx::mbar_init(&o_done[s], 1);
     }
     ptx::mbar_init(drain, 1);
-    ptx::mbar_init(xbar, 256);
+    ptx::mbar_init(xbar, 8);                              // one arrival per softmax warp
     ptx::mbar_init(l_ready, 8);
     ptx::mbar_init(&o_free[0], p.use_tma ? 128 : 256);   // whoever runs the epilogue
     ptx::mbar_init(&o_free[1], p.use_tma ? 128 : 256);
@@ -421,8 +421,9 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           const float my_max = sm::row_max(s);
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 5);
           xch_max[ph & 1][half][row] = my_max;
-          ptx::mbar_arrive(xbar);                         // rendezvous of all 256 softmax threads (bounded,
-          ok = ptx::mbar_wait(xbar, ph & 1, abort_p);     // unlike bar.sync); also: everyone has read S
+          __syncwarp();                                   // rendezvous of all 8 softmax warps (bounded, unlike
+          if (lane == 0) ptx::mbar_arrive(xbar);          // bar.sync): one arrival per warp
+          ok = ptx::mbar_wait(xbar, ph & 1, abort_p);     // also: everyone has finished reading S
           if (!ok) { if (*abort_p == 1) *abort_p = 17; break; }
           const float tile_max = fmaxf(my_max, xch_max[ph & 1][half ^ 1][row]);
           ++ph;
@@ -480,7 +481,8 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
         ++n_done;
         continue;
       }
-      ptx::mbar_arrive(xbar);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(xbar);
       ok = ptx::mbar_wait(xbar, ph & 1, abort_p);
       if (!ok) { if (*abort_p == 1) *abort_p = 18; break; }
       ++ph;
