@@ -3,13 +3,13 @@
 // memory. While one sub-tile's softmax runs on the CUDA cores, the tensor core works on the
 // other's QK^T and PV, so the two pipes overlap inside one CTA:
 //
-//   warps 0-7    softmax / correction / epilogue, alternating between the sub-tiles: warps 0-3 own score
-//                columns 0-63 and warps 4-7 columns 64-127 of every row of BOTH sub-tiles
+//   softmax warps (8 or 16)  softmax / correction, alternating between the sub-tiles: warpgroup j owns score
+//                columns [j * 128 / NSPLIT, (j + 1) * 128 / NSPLIT) of every row of BOTH sub-tiles
 //                (TMEM: S0 cols 0-127, S1 cols 128-255, O0 cols 256-383, O1 cols 384-511)
-//   warps 8-11   when the tiles are TMA boxes: epilogue warps (O of a finished item -> bf16 -> global while
+//   next 4 warps when the tiles are TMA boxes: epilogue warps (O of a finished item -> bf16 -> global while
 //                the softmax warps are already on the next item); otherwise loaders: index maps +
 //                cp.async row gathers, completion signalled by the copies themselves
-//   warp 13      one thread issues the TMA loads of Q0, Q1 and a 2-stage ring each for K, V
+//   then: a warp whose elected thread issues tcgen05.mma (below) and a warp with one thread that issues the TMA loads of Q0, Q1 and a 2-stage ring each for K, V
 //   warp 12      one thread issues tcgen05.mma in the order QK0(n) PV1(n-1) QK1(n) PV0(n), carried on
 //                across tile boundaries so the next tile's first QK^T overlaps this tile's last softmax
 //
@@ -45,7 +45,21 @@ __device__ long long g_trace_item[4 * 32 * 8];
 #define INTRA_TRACE_ITEM(cond, role, ev) do {} while (0)
 #endif
 
-constexpr int DUAL_THREADS = 512;
+// Softmax column split: each query row of a sub-tile is shared by NSPLIT threads (one per softmax
+// warpgroup), 128 / NSPLIT score columns each. Two instantiations: NSPLIT = 4 (768 threads) hides more
+// latency and wins on short items, NSPLIT = 2 (512 threads) leaves the MMA-issuing warp's scheduler
+// less crowded and wins on long ones; the host picks by the key tiles per item.
+template <int NSPLIT>
+struct DualCfg {
+  static_assert(NSPLIT == 2 || NSPLIT == 4, "softmax column split must be 2 or 4");
+  static constexpr int COLS = TILE_N / NSPLIT;            // score columns per softmax thread
+  static constexpr int SM_WARPS = 4 * NSPLIT;             // softmax warps
+  static constexpr int SM_THREADS = 128 * NSPLIT;
+  static constexpr int THREADS = SM_THREADS + 256;        // + epilogue / loader warpgroup + MMA / TMA warpgroup
+  static constexpr int SM_REGS = NSPLIT == 2 ? 192 : 88;  // setmaxnreg budgets: softmax, epilogue / loaders, MMA / TMA
+  static constexpr int EP_REGS = 64;
+  static constexpr int MMA_REGS = NSPLIT == 2 ? 64 : 48;
+};
 constexpr int KV_STAGES = 2;
 constexpr int DUAL_SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + 1024;   // Q0 Q1 | K ring | V ring
 constexpr int DUAL_TMEM_COLS = 512;
@@ -286,7 +300,11 @@ __device__ __forceinline__ void split_loader(const DualParams& p, const SplitLoa
   if (!kTma) { ptx::cp_async_commit(); ptx::cp_async_wait<0>(); }
 }
 
-__global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const __grid_constant__ DualParams p) {
+template <int NSPLIT>
+__global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_kernel(const __grid_constant__ DualParams p) {
+  using Cfg = DualCfg<NSPLIT>;
+  constexpr int COLS = Cfg::COLS, SM_WARPS = Cfg::SM_WARPS, SM_THREADS = Cfg::SM_THREADS;
+  constexpr int SM_REGS = Cfg::SM_REGS, EP_REGS = Cfg::EP_REGS, MMA_REGS = Cfg::MMA_REGS;
   extern __shared__ uint8_t smem_raw[];
   // barriers: 0 q_full, 1-2 k_full, 3-4 v_full, 5 s0_full, 6-7 s1_full[stage], 8-9 p_full[s],
   //           10-11 o_done[s], 12 drain, 13 xbar (softmax threads' exchange rendezvous),
@@ -294,8 +312,8 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
   __shared__ uint64_t bars[17];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
-  __shared__ float xch_max[2][2][TILE_M];      // [phase parity][column half][row]: partial row maxima
-  __shared__ float xch_sum[2][2][2][TILE_M];   // [item parity][sub-tile][column half][row]: partial row sums
+  __shared__ float xch_max[2][NSPLIT][TILE_M];      // [phase parity][column part][row]: partial row maxima
+  __shared__ float xch_sum[2][2][NSPLIT][TILE_M];   // [item parity][sub-tile][column part][row]: partial row sums
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -334,14 +352,14 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
     ptx::mbar_init(s0_full, 1);
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&s1_full[s], 1);
-      ptx::mbar_init(&p_full[s], 256);
+      ptx::mbar_init(&p_full[s], SM_WARPS);               // one arrival per softmax warp
       ptx::mbar_init(&o_done[s], 1);
     }
     ptx::mbar_init(drain, 1);
-    ptx::mbar_init(xbar, 8);                              // one arrival per softmax warp
-    ptx::mbar_init(l_ready, 8);
-    ptx::mbar_init(&o_free[0], p.use_tma ? 128 : 256);   // whoever runs the epilogue
-    ptx::mbar_init(&o_free[1], p.use_tma ? 128 : 256);
+    ptx::mbar_init(xbar, SM_WARPS);                       // one arrival per softmax warp
+    ptx::mbar_init(l_ready, SM_WARPS);
+    ptx::mbar_init(&o_free[0], p.use_tma ? 128 : SM_THREADS);   // whoever runs the epilogue
+    ptx::mbar_init(&o_free[1], p.use_tma ? 128 : SM_THREADS);
     ptx::fence_mbar_init();
   }
   if (warp == 0) {
@@ -364,14 +382,14 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
     if (!ok) { if (*abort_p == 1) *abort_p = (code); }                              \
   } while (0)
 
-  if (warp < 8) {
+  if (warp < SM_WARPS) {
     // ================================ softmax / correction / epilogue ==========================
-    // All eight warps work on ONE sub-tile at a time, alternating between the two: thread (half, row)
-    // owns the 64 score columns `half` of query row `row` of both sub-tiles. Two warps per scheduler
-    // then hide each other's latencies while the tensor core works on the other sub-tile. The two
-    // halves of a row agree on the row maximum through shared memory and a 256-arrival mbarrier.
-    ptx::setmaxnreg_inc<192>();
-    const int half = warp >> 2;                           // which 64 columns of every score tile
+    // All softmax warps work on ONE sub-tile at a time, alternating between the two: thread (part, row)
+    // owns the COLS score columns `part` of query row `row` of both sub-tiles. NSPLIT warps per
+    // scheduler then hide each other's latencies while the tensor core works on the other sub-tile.
+    // The parts of a row agree on the row maximum through shared memory and a bounded mbarrier.
+    ptx::setmaxnreg_inc<SM_REGS>();
+    const int half = warp >> 2;                           // which COLS columns of every score tile
     const int row = tid & 127;                            // TMEM lane == query row
     const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
     const float scale_log2 = p.f.scale_log2;
@@ -402,18 +420,19 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           ptx::tc_fence_after();
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 0);
           const uint32_t s_addr = lane_addr + sx * 128;
-          const uint32_t o_addr = lane_addr + 256 + sx * 128 + half * 64;
+          const uint32_t o_addr = lane_addr + 256 + sx * 128 + half * COLS;
 
-          float s[64];
-          ptx::tmem_ld32(s_addr + half * 64, reinterpret_cast<uint32_t*>(s));
-          ptx::tmem_ld32(s_addr + half * 64 + 32, reinterpret_cast<uint32_t*>(s) + 32);
+          float s[COLS];
+#pragma unroll
+          for (int c = 0; c < COLS / 32; ++c)
+            ptx::tmem_ld32(s_addr + half * COLS + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
           ptx::tmem_wait_ld();
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 1);
 
-          const int u0 = n * TILE_N + half * 64;
-          if (lo[sx] > u0 || hi[sx] < u0 + 63) {          // this row's interval does not cover these columns
+          const int u0 = n * TILE_N + half * COLS;
+          if (lo[sx] > u0 || hi[sx] < u0 + COLS - 1) {    // this row's interval does not cover these columns
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
+            for (int c = 0; c < COLS; ++c) {
               const int u = u0 + c;
               if (u < lo[sx] || u > hi[sx]) s[c] = -CUDART_INF_F;
             }
@@ -425,7 +444,9 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           if (lane == 0) ptx::mbar_arrive(xbar);          // bar.sync): one arrival per warp
           ok = ptx::mbar_wait(xbar, ph & 1, abort_p);     // also: everyone has finished reading S
           if (!ok) { if (*abort_p == 1) *abort_p = 17; break; }
-          const float tile_max = fmaxf(my_max, xch_max[ph & 1][half ^ 1][row]);
+          float tile_max = my_max;
+#pragma unroll
+          for (int o = 1; o < NSPLIT; ++o) tile_max = fmaxf(tile_max, xch_max[ph & 1][(half + o) % NSPLIT][row]);
           ++ph;
           const float m_new = fmaxf(m_run[sx], tile_max);
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 2);
@@ -442,7 +463,7 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
             // The previous key tile's PV was issued before the QK^T whose completion was just waited
             // for, and the tensor pipe completes in order: O is quiescent here.
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < COLS / 16; ++c) {
               uint32_t o[16];
               ptx::tmem_ld16(o_addr + c * 16, o);
               ptx::tmem_wait_ld();
@@ -454,17 +475,18 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           const float base = (m_run[sx] == -CUDART_INF_F) ? 0.f : m_run[sx] * scale_log2;
           sm::f2 sum[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-          for (int c2 = 0; c2 < 2; ++c2) {                // 32 scores -> 16 packed columns of P
+          for (int c2 = 0; c2 < COLS / 32; ++c2) {        // 32 scores -> 16 packed columns of P
             uint32_t pk[16];
             sm::exp_chunk(s, c2 * 32, scale_log2, base, pk, sum);
-            ptx::tmem_st16(s_addr + half * 32 + c2 * 16, pk);
+            ptx::tmem_st16(s_addr + half * (COLS / 2) + c2 * 16, pk);
             INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 6 + c2);
           }
           l_part[sx] += sm::sum4(sum);
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 3);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
-          ptx::mbar_arrive(&p_full[sx]);
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&p_full[sx]);
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 4);
         }
       }
@@ -493,12 +515,14 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
         if (!ok) { if (*abort_p == 1) *abort_p = 15 + sx; break; }
         ptx::tc_fence_after();
         INTRA_TRACE_ITEM(tid == 0, 1, 4 + 2 * sx);
-        const float l_tot = l_part[sx] + xch_sum[ipar][sx][half ^ 1][row];
+        float l_tot = l_part[sx];
+#pragma unroll
+        for (int o = 1; o < NSPLIT; ++o) l_tot += xch_sum[ipar][sx][(half + o) % NSPLIT][row];
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
         const int h = sx ? di.h1 : di.h0;
         const int tk = token[sx];
-        __nv_bfloat16* dst = p.f.o + di.b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh + half * 64;
-        store_o_row(lane_addr + 256 + sx * 128 + half * 64, 64, inv, dst, tk >= 0, p.wide_stores != 0);
+        __nv_bfloat16* dst = p.f.o + di.b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh + half * COLS;
+        store_o_row(lane_addr + 256 + sx * 128 + half * COLS, COLS, inv, dst, tk >= 0, p.wide_stores != 0);
         ptx::tc_fence_before();
         ptx::mbar_arrive(&o_free[sx]);
       }
@@ -506,10 +530,10 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
       ++n_done;
       INTRA_TRACE_ITEM(tid == 0, 1, 2);
     }
-  } else if (warp < 12) {
-    // ================================ loaders ===================================================
-    ptx::setmaxnreg_dec<64>();
-    const int lt = tid - 256;
+  } else if (warp < SM_WARPS + 4) {
+    // ================================ epilogue warps / loaders =====================================
+    ptx::setmaxnreg_dec<EP_REGS>();
+    const int lt = tid - SM_THREADS;
     uint32_t kc = 0;                                      // K / V tiles loaded so far (ring position)
     bool ok = true;
     int n_done = 0;
@@ -535,7 +559,9 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
           ok = ptx::mbar_wait(&o_done[sx], ipar, abort_p);         // last PV of this item
           if (!ok) { if (*abort_p == 1) *abort_p = 42 + sx; break; }
           ptx::tc_fence_after();
-          const float l_tot = xch_sum[ipar][sx][0][row] + xch_sum[ipar][sx][1][row];
+          float l_tot = 0.f;
+#pragma unroll
+          for (int o = 0; o < NSPLIT; ++o) l_tot += xch_sum[ipar][sx][o][row];
           const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
           const int h = sx ? di.h1 : di.h0;
           const int tk = token[sx];
@@ -621,11 +647,11 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
     }
   } else {
     // ================================ MMA issue ==================================================
-    ptx::setmaxnreg_dec<64>();
-    if (warp == 13 && p.use_tma && lane == 0 && p.split_kv) {
+    ptx::setmaxnreg_dec<MMA_REGS>();
+    if (warp == SM_WARPS + 5 && p.use_tma && lane == 0 && p.split_kv) {
       const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, k_full, v_full, s0_full, s1_full, abort_p};
       split_loader<true>(p, cx, cta, n_cta, 0);
-    } else if (warp == 13 && p.use_tma && lane == 0) {
+    } else if (warp == SM_WARPS + 5 && p.use_tma && lane == 0) {
       // ---- one thread drives the TMA unit ------------------------------------------------------------
       uint32_t kc = 0;                                    // K / V tiles requested so far (ring position)
       bool ok = true;
@@ -661,19 +687,23 @@ __global__ void __launch_bounds__(DUAL_THREADS, 1) intra_fwd_dual_kernel(const _
             INTRA_WAIT_TILE_DONE(kc - 2, 22);
             if (!ok) break;
           }
+          INTRA_TRACE_EV(true, 3, n, 0);
           ptx::mbar_arrive_expect_tx(&k_full[stage], TILE_BYTES);
           tma_fetch_kv(p.f.prob, di.pt.kv, n, di.hk, di.b, k_op, k_smem0 + stage * TILE_BYTES, &k_full[stage]);
+          INTRA_TRACE_EV(true, 3, n, 1);
           if (kc >= 2) {                                // V stage: PV1 of key tile kc-2, issued before QK1 of kc-1
             INTRA_WAIT_TILE_DONE(kc - 1, 23);
             if (!ok) break;
           }
+          INTRA_TRACE_EV(true, 3, n, 2);
           ptx::mbar_arrive_expect_tx(&v_full[stage], TILE_BYTES);
           tma_fetch_kv(p.f.prob, di.pt.kv, n, di.hk, di.b, v_op, v_smem0 + stage * TILE_BYTES, &v_full[stage]);
+          INTRA_TRACE_EV(true, 3, n, 3);
         }
         ++n_done;
       }
     }
-    if (warp == 12) {
+    if (warp == SM_WARPS + 4) {
       uint32_t kc = 0;                                    // key tiles issued so far
       uint32_t it0 = 0, it1 = 0;                          // PVs issued per sub-tile (p_full phases)
       const uint64_t q0_desc = tile_desc_kmajor(q_smem0), q1_desc = tile_desc_kmajor(q_smem0 + TILE_BYTES);

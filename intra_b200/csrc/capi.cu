@@ -64,7 +64,9 @@ void init_device(int device) {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
   st.sm_count = prop.multiProcessorCount;
   if (e == cudaSuccess) e = cudaMalloc(&st.status_word, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(st.status_word, 0, sizeof(int));
@@ -284,7 +286,18 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
                 build_maps(p.prob, p.k, p.ks, Hkv, B, false, &d.maps.k_main, &d.maps.k_text, &d.maps.k_aux) &&
                 build_maps(p.prob, p.v, p.vs, Hkv, B, false, &d.maps.v_main, &d.maps.v_text, &d.maps.v_aux);
     const int grid = static_cast<int>(items < g_dev[device].sm_count ? items : g_dev[device].sm_count);
-    intra_fwd_dual_kernel<<<grid, DUAL_THREADS, DUAL_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(d);
+    // Softmax column split (attn_kernel_dual.cuh): 4-way for short items, 2-way for long ones.
+    int64_t n_tiles = 0, n_kv = 0;
+    for (int idx = 0; idx < d.n_pair_tiles; ++idx) {
+      const int t = make_pair(p.prob, d.row_pairs, idx).kv.n_kv_tiles;
+      if (t > 0) { ++n_tiles; n_kv += t; }
+    }
+    static const int force_split = [] { const char* v = std::getenv("INTRA_B200_SOFTMAX_SPLIT"); return v ? std::atoi(v) : 0; }();
+    const bool four = force_split ? force_split == 4 : (n_tiles > 0 && n_kv < 24 * n_tiles);
+    if (four)
+      intra_fwd_dual_kernel<4><<<grid, DualCfg<4>::THREADS, DUAL_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(d);
+    else
+      intra_fwd_dual_kernel<2><<<grid, DualCfg<2>::THREADS, DUAL_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(d);
   } else {
     intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
   }

@@ -1,10 +1,11 @@
-// Register-level pieces of the online softmax one thread runs over its query row: a 128-wide score
-// tile lives in 128 registers (read from tensor memory) and is turned into 64 registers of packed
-// bf16 probabilities.
+// Register-level pieces of the online softmax a thread runs over its share of a query row: 32 or 64
+// score columns live in registers (read from tensor memory) and are turned into packed bf16
+// probabilities.
 //
-// The work is arranged for a single warp per scheduler with nobody to hide its latencies behind:
+// The work is arranged so that a warp depends as little as possible on others to hide its latencies:
 //   * row maximum: four independent chains of three-input max instead of one 127-deep chain;
-//   * scale-and-shift and the row sum use the packed two-lane fp32 instructions (fma/add.f32x2);
+//   * the row sum uses the packed two-lane add (add.f32x2); multiply-adds stay scalar, which is the
+//     cheaper form on this part (see ex2_fma_pipe);
 //   * exponentials are split between the two pipes that can produce them: most go to the MUFU
 //     (ex2.approx, 16 results per clock per SM), a fixed share is computed on the FMA pipe with a
 //     floor / degree-3-polynomial / exponent-add evaluation of 2^x whose relative error (8.6e-5) is far
@@ -75,33 +76,34 @@ __device__ __forceinline__ float row_max(const float (&s)[N]) {
   return max3(a0, a1, fmaxf(a2, a3));
 }
 
-// 2^x for both lanes on the FMA pipe, for x <= 127: floor(x) by a round-down add of 1.5 * 2^23, the
+// 2^x for two values on the FMA pipe, for x <= 127: floor(x) by a round-down add of 1.5 * 2^23, the
 // fraction f = x - floor(x) in [0, 1) through a cubic fitted to 2^f (max relative error 8.6e-5), and
 // floor(x) added straight into the exponent field. Inputs below -126 (masked scores are -inf) are
 // clamped, which yields 2^-126, i.e. zero for every purpose here.
-__device__ __forceinline__ f2 ex2_fma_pipe(f2 x) {
+// Measured on B200 (clocks per warp instruction per scheduler): fma.rn.f32x2 3.0 against 0.75 for a
+// scalar fma, add/sub.f32x2 2.0, 3-input max 2.0, ex2.approx 8.0. So the packed form is used where it
+// saves issue slots cheaply (the three add/subs) and the multiply-adds stay scalar.
+__device__ __forceinline__ void ex2_fma_pipe(float x0, float x1, float& r0, float& r1) {
   constexpr float kMagic = 12582912.f;
-  float x0, x1;
-  unpack2(x, x0, x1);
   const f2 xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
   const f2 magic = pack2(kMagic, kMagic);
   const f2 t = add2_rm(xc, magic);
-  const f2 fl = sub2(t, magic);
-  const f2 f = sub2(xc, fl);
-  f2 p = fma2(f, pack2(0.07706704f, 0.07706704f), pack2(0.22764499f, 0.22764499f));
-  p = fma2(p, f, pack2(0.69511676f, 0.69511676f));
-  p = fma2(p, f, pack2(1.f, 1.f));
-  float p0, p1, t0, t1;
-  unpack2(p, p0, p1);
+  const f2 f = sub2(xc, sub2(t, magic));
+  float f0, f1, t0, t1;
+  unpack2(f, f0, f1);
   unpack2(t, t0, t1);
-  const float r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  const float r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
-  return pack2(r0, r1);
+  float p0 = fmaf(f0, 0.07706704f, 0.22764499f), p1 = fmaf(f1, 0.07706704f, 0.22764499f);
+  p0 = fmaf(p0, f0, 0.69511676f);
+  p1 = fmaf(p1, f1, 0.69511676f);
+  p0 = fmaf(p0, f0, 1.f);
+  p1 = fmaf(p1, f1, 1.f);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
 // Which of every 8 consecutive score pairs take the FMA-pipe exponential (bit i = pair i).
 #ifndef INTRA_EX2_FMA_MASK
-#define INTRA_EX2_FMA_MASK 0x94u   // pairs 2, 4, 7: three of eight
+#define INTRA_EX2_FMA_MASK 0x88u   // pairs 3 and 7: two of eight
 #endif
 
 // p[c] = 2^(s[c] * scale_log2 - base) for 32 scores starting at s[first]; returns their 16 packed
@@ -109,24 +111,19 @@ __device__ __forceinline__ f2 ex2_fma_pipe(f2 x) {
 template <int N>
 __device__ __forceinline__ void exp_chunk(const float (&s)[N], int first, float scale_log2, float base,
                                           uint32_t (&pk)[16], f2 (&sum)[4]) {
-  const f2 scale2 = pack2(scale_log2, scale_log2);
-  const f2 nbase2 = pack2(-base, -base);
+  const float nbase = -base;
 #pragma unroll
   for (int c = 0; c < 16; ++c) {
-    const f2 x = fma2(pack2(s[first + 2 * c], s[first + 2 * c + 1]), scale2, nbase2);
-    f2 p;
+    const float x0 = fmaf(s[first + 2 * c], scale_log2, nbase);
+    const float x1 = fmaf(s[first + 2 * c + 1], scale_log2, nbase);
     float p0, p1;
     if ((INTRA_EX2_FMA_MASK >> (c & 7)) & 1u) {
-      p = ex2_fma_pipe(x);
-      unpack2(p, p0, p1);
+      ex2_fma_pipe(x0, x1, p0, p1);
     } else {
-      float x0, x1;
-      unpack2(x, x0, x1);
       p0 = ptx::ex2(x0);
       p1 = ptx::ex2(x1);
-      p = pack2(p0, p1);
     }
-    sum[c & 3] = add2(sum[c & 3], p);
+    sum[c & 3] = add2(sum[c & 3], pack2(p0, p1));
     pk[c] = ptx::pack_bf16(p0, p1);
   }
 }
