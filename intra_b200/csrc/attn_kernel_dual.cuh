@@ -300,7 +300,7 @@ __device__ __forceinline__ void split_loader(const DualParams& p, const SplitLoa
   if (!kTma) { ptx::cp_async_commit(); ptx::cp_async_wait<0>(); }
 }
 
-template <int NSPLIT>
+template <int NSPLIT, bool kSplitKV>
 __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_kernel(const __grid_constant__ DualParams p) {
   using Cfg = DualCfg<NSPLIT>;
   constexpr int COLS = Cfg::COLS, SM_WARPS = Cfg::SM_WARPS, SM_THREADS = Cfg::SM_THREADS;
@@ -352,7 +352,11 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     ptx::mbar_init(s0_full, 1);
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&s1_full[s], 1);
+#ifdef INTRA_PFULL_PER_THREAD
+      ptx::mbar_init(&p_full[s], SM_THREADS);
+#else
       ptx::mbar_init(&p_full[s], SM_WARPS);               // one arrival per softmax warp
+#endif
       ptx::mbar_init(&o_done[s], 1);
     }
     ptx::mbar_init(drain, 1);
@@ -485,8 +489,12 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 3);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
+#ifdef INTRA_PFULL_PER_THREAD
+          ptx::mbar_arrive(&p_full[sx]);
+#else
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(&p_full[sx]);
+#endif
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 4);
         }
       }
@@ -572,7 +580,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
         }
         ++n_done;
       }
-    } else if (p.split_kv) {
+    } else if (kSplitKV) {
       const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, k_full, v_full, s0_full, s1_full, abort_p};
       split_loader<false>(p, cx, cta, n_cta, lt);
     } else {
@@ -648,7 +656,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
   } else {
     // ================================ MMA issue ==================================================
     ptx::setmaxnreg_dec<MMA_REGS>();
-    if (warp == SM_WARPS + 5 && p.use_tma && lane == 0 && p.split_kv) {
+    if (kSplitKV && warp == SM_WARPS + 5 && p.use_tma && lane == 0) {
       const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, k_full, v_full, s0_full, s1_full, abort_p};
       split_loader<true>(p, cx, cta, n_cta, 0);
     } else if (warp == SM_WARPS + 5 && p.use_tma && lane == 0) {
@@ -728,8 +736,8 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
         INTRA_TRACE_ITEM(lane == 0, 0, 1);
         for (int n = 0; n < n_kv; ++n, ++kc) {
           // shared keys: both sub-tiles read ring stage kc % 2; split keys: sub-tile s reads buffer s
-          const int stage = p.split_kv ? 0 : kc % KV_STAGES;
-          const uint32_t par = p.split_kv ? (kc & 1) : (kc / KV_STAGES) & 1;
+          const int stage = kSplitKV ? 0 : kc % KV_STAGES;
+          const uint32_t par = kSplitKV ? (kc & 1) : (kc / KV_STAGES) & 1;
           ok = ptx::mbar_wait(&k_full[stage], par, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 32; break; }
           ptx::fence_proxy_async_smem();
@@ -748,7 +756,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
               ok = ptx::mbar_wait(&o_free[1], (pend_item - 1) & 1, abort_p);
               if (!ok) { if (*abort_p == 1) *abort_p = 38; break; }
             }
-            if (p.split_kv) {                             // sub-tile 1's own V buffer
+            if (kSplitKV) {                               // sub-tile 1's own V buffer
               ok = ptx::mbar_wait(&v_full[1], (kc - 1) & 1, abort_p);
               if (!ok) { if (*abort_p == 1) *abort_p = 40; break; }
               ptx::fence_proxy_async_smem();
@@ -763,14 +771,14 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             ++it1;
             pend = false;
           }
-          if (p.split_kv) {                               // sub-tile 1's own K buffer
+          if (kSplitKV) {                                 // sub-tile 1's own K buffer
             ok = ptx::mbar_wait(&k_full[1], par, abort_p);
             if (!ok) { if (*abort_p == 1) *abort_p = 41; break; }
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_after();
           }
           if (ptx::elect_one()) {
-            issue_qk_desc(q1_desc, p.split_kv ? k_desc0 + kStageStep : k_desc, tmem + 128);
+            issue_qk_desc(q1_desc, kSplitKV ? k_desc0 + kStageStep : k_desc, tmem + 128);
             ptx::mma_commit(&s1_full[kc & 1]);
           }
           __syncwarp();
@@ -797,7 +805,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           pend = true;
           pend_last = (n == n_kv - 1);
           pend_acc = n > 0 ? 1u : 0u;
-          pend_stage = p.split_kv ? 1 : stage;
+          pend_stage = kSplitKV ? 1 : stage;
           pend_item = n_done;
         }
         INTRA_TRACE_ITEM(lane == 0, 0, 2);
@@ -810,7 +818,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           ok = ptx::mbar_wait(&o_free[1], (pend_item - 1) & 1, abort_p);
           if (!ok && *abort_p == 1) *abort_p = 39;
         }
-        if (ok && p.split_kv) {
+        if (ok && kSplitKV) {
           ok = ptx::mbar_wait(&v_full[1], (kc - 1) & 1, abort_p);
           if (!ok && *abort_p == 1) *abort_p = 40;
           ptx::fence_proxy_async_smem();

@@ -64,9 +64,13 @@ void init_device(int device) {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
   st.sm_count = prop.multiProcessorCount;
   if (e == cudaSuccess) e = cudaMalloc(&st.status_word, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(st.status_word, 0, sizeof(int));
@@ -294,10 +298,11 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
     }
     static const int force_split = [] { const char* v = std::getenv("INTRA_B200_SOFTMAX_SPLIT"); return v ? std::atoi(v) : 0; }();
     const bool four = force_split ? force_split == 4 : (n_tiles > 0 && n_kv < 24 * n_tiles);
-    if (four)
-      intra_fwd_dual_kernel<4><<<grid, DualCfg<4>::THREADS, DUAL_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(d);
-    else
-      intra_fwd_dual_kernel<2><<<grid, DualCfg<2>::THREADS, DUAL_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(d);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (four && d.split_kv) intra_fwd_dual_kernel<4, true><<<grid, DualCfg<4>::THREADS, DUAL_SMEM_BYTES, st>>>(d);
+    else if (four) intra_fwd_dual_kernel<4, false><<<grid, DualCfg<4>::THREADS, DUAL_SMEM_BYTES, st>>>(d);
+    else if (d.split_kv) intra_fwd_dual_kernel<2, true><<<grid, DualCfg<2>::THREADS, DUAL_SMEM_BYTES, st>>>(d);
+    else intra_fwd_dual_kernel<2, false><<<grid, DualCfg<2>::THREADS, DUAL_SMEM_BYTES, st>>>(d);
   } else {
     intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
   }
