@@ -233,3 +233,18 @@ def test_flux_caller_and_relaxed_shapes(lib):
             assert _util.max_abs_err(out, ref) <= _util.ATOL
         with pytest.raises(ValueError):
             intra_image_attn(qi, ki, vi, "scatter", 48)
+
+
+@pytest.mark.parametrize("gain", [6.0, 24.0])
+def test_large_logits_exercise_rescaling(lib, gain):
+    """Scores spread over hundreds of units (large-magnitude q): the running maximum moves many times,
+    accumulators are rescaled in tensor memory, and most probabilities underflow to zero."""
+    q, k, v = oracle.make_inputs(1, 3072, 4, 2, seed=17, device="cuda")
+    q = (q.float() * gain).to(torch.bfloat16)
+    for pattern, param, mask in (("scatter", 2, oracle.llm_scatter_mask(3072, 2)),
+                                 ("window", 576, oracle.llm_window_mask(3072, 576))):
+        rc, out = _util.call_fwd(lib, "llm", pattern, q, k, v, param)
+        assert rc == 0
+        ref = _util.oracle_attention(q, k, v, mask, on_device=True)
+        assert bool(torch.isfinite(out).all())
+        assert _util.max_abs_err(out, ref) <= 2 * _util.ATOL   # near one-hot rows: a bf16 ulp of |v| <= 4
