@@ -12,7 +12,8 @@ call and one window-576 call. Rank 0 prints ONE JSON line:
               summed over all ranks (each rank runs its own batch: weak scaling), inputs resident in
               HBM, CUDA events on the launching stream, max over ranks
   e2e         the same metric through the public Python API with pinned HOST buffers: per step the
-              q/k/v host->device copies, both calls, and the device->host copy of both outputs
+              q/k/v host->device copies, both calls, and the device->host copy of both outputs; steps
+              are pipelined over three streams (copy-in, kernels, copy-out)
   roofline    tensor-core roofline of the dominant launch (the Gather-1 call): algorithmic FLOPs per
               launch / its mean CUDA-event duration inside the timed region, against the measured
               bf16 dense peak of MEASURED_PEAKS.json
@@ -310,19 +311,51 @@ def run_ours(args):
         launch_ms = [statistics.mean(evs[s][i][0].elapsed_time(evs[s][i][1]) for s in range(args.steps))
                      for i in range(len(calls))]
 
-        # ---- end-to-end: pinned host buffers in, host buffers out, every step
+        # ---- end-to-end: pinned host buffers in, host buffers out, every step. Three streams pipeline
+        # the steps: the copy-in of step i+1 and the copy-out of step i-1 run beside step i's kernels
+        # (PCIe is full duplex), with device buffers double-buffered. Every step still copies its own
+        # inputs in and its own outputs out.
         e_steps = max(3, min(args.steps, 20))
-        for _ in range(2):
-            dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
-            for i, c in enumerate(calls):
-                houts[i].copy_(run_call(c, dq, dk, dv), non_blocking=True)
+        s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        dbuf = [(torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)) for _ in range(2)]
+        ev_in = [torch.cuda.Event() for _ in range(2)]      # inputs of the slot have landed
+        ev_cmp = [torch.cuda.Event() for _ in range(2)]     # kernels of the slot are done (inputs reusable)
+        ev_out = [torch.cuda.Event() for _ in range(2)]     # outputs of the slot are on the host
+
+        def e2e_steps(n_steps):
+            for st in range(n_steps):
+                slot = st & 1
+                with torch.cuda.stream(s_in):
+                    if st >= 2:
+                        s_in.wait_event(ev_cmp[slot])
+                    dbuf[slot][0].copy_(hq, non_blocking=True)
+                    dbuf[slot][1].copy_(hk, non_blocking=True)
+                    dbuf[slot][2].copy_(hv, non_blocking=True)
+                    ev_in[slot].record(s_in)
+                with torch.cuda.stream(s_cmp):
+                    s_cmp.wait_event(ev_in[slot])
+                    outs = [run_call(c, *dbuf[slot]) for c in calls]
+                    ev_cmp[slot].record(s_cmp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_cmp[slot])
+                    for i, o in enumerate(outs):
+                        houts[i].copy_(o, non_blocking=True)
+                        o.record_stream(s_out)
+                    ev_out[slot].record(s_out)
+
+        for st_ in (s_in, s_cmp, s_out):
+            st_.wait_stream(stream)
+        e2e_steps(2)
+        for st_ in (s_in, s_cmp, s_out):
+            stream.wait_stream(st_)
         e_beg, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e_beg.record(stream)
-        for _ in range(e_steps):
-            dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
-            for i, c in enumerate(calls):
-                houts[i].copy_(run_call(c, dq, dk, dv), non_blocking=True)
+        for st_ in (s_in, s_cmp, s_out):
+            st_.wait_stream(stream)
+        e2e_steps(e_steps)
+        for st_ in (s_in, s_cmp, s_out):
+            stream.wait_stream(st_)
         e_end.record(stream)
         barrier()
         e2e_ms = e_beg.elapsed_time(e_end)
