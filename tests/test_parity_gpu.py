@@ -248,3 +248,29 @@ def test_large_logits_exercise_rescaling(lib, gain):
         ref = _util.oracle_attention(q, k, v, mask, on_device=True)
         assert bool(torch.isfinite(out).all())
         assert _util.max_abs_err(out, ref) <= 2 * _util.ATOL   # near one-hot rows: a bf16 ulp of |v| <= 4
+
+
+def test_llm_backend_callable(lib):
+    """The transformers-style attention callable: layer schedule, (B, H, S, D) inputs, prefill on the
+    kernels, dense decode step."""
+    from intra_b200 import llm_backend
+
+    class Layer:
+        def __init__(self, idx):
+            self.layer_idx = idx
+
+    assert [llm_backend.layer_masktype(i) for i in range(6)] == [0, 0, 4, 4, 0, 0]
+    fn = llm_backend.make_intra_attention()
+    g = torch.Generator().manual_seed(12)
+    q = torch.randn(1, 8, 1024, 128, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(1, 2, 1024, 128, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(1, 2, 1024, 128, generator=g).to(torch.bfloat16).cuda()
+    for idx, mask in ((1, oracle.llm_scatter_mask(1024, 8)), (2, oracle.llm_window_mask(1024, 576))):
+        out, w = fn(Layer(idx), q, k, v, scaling=128 ** -0.5)
+        assert w is None and out.shape == (1, 1024, 8, 128)
+        ref = _util.oracle_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), mask, on_device=True)
+        assert _util.max_abs_err(out, ref) <= _util.ATOL
+    out, _ = fn(Layer(0), q[:, :, -1:], k, v, scaling=128 ** -0.5)     # decode step: dense over the cache
+    kk, vv = k.repeat_interleave(4, 1).float(), v.repeat_interleave(4, 1).float()
+    att = torch.softmax(q[:, :, -1:].float() @ kk.transpose(-1, -2) * 128 ** -0.5, -1) @ vv
+    assert _util.max_abs_err(out, att.transpose(1, 2)) <= _util.ATOL
