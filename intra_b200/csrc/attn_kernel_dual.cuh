@@ -190,6 +190,143 @@ __device__ __forceinline__ void store_o_row(uint32_t o_addr, int ncols, float in
   }
 }
 
+// Box coordinates of an item's key tiles are affine in the tile number within at most two segments
+// (image kinds: the 512 text keys, then the image keys). The TMA thread works them out once per item
+// and afterwards only adds a constant per tile: it shares a scheduler with softmax warps, and every
+// instruction it spends per tile slows those down.
+struct KvSegment {
+  int c[5];          // coordinates of the segment's first tile (c[0] unused)
+  int d[5];          // increment per tile
+  int first;         // first tile of the segment
+  int text;          // 1: text map (rank 4), 0: main / aux map
+  int rank4;
+};
+__device__ __forceinline__ void kv_segment(const Problem& prob, const Tile& kv, int first, int n_kv, int head, int batch,
+                                           KvSegment* sg) {
+  int start; bool text;
+  tma_kv_start(kv, first, &start, &text);
+  sg->first = first;
+  sg->text = tma_box_coords(prob, kv, start, text, head, batch, sg->c);
+  sg->rank4 = sg->text || kv.kind == KIND_LLM_WINDOW;
+  int c1[5];
+  if (first + 1 < n_kv) {
+    tma_kv_start(kv, first + 1, &start, &text);
+    tma_box_coords(prob, kv, start, text, head, batch, c1);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 5; ++i) c1[i] = sg->c[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 5; ++i) sg->d[i] = c1[i] - sg->c[i];
+}
+__device__ __forceinline__ void tma_fetch_planned(const KvSegment& sg, int n, const CUtensorMap* m, uint32_t dst,
+                                                  uint64_t* bar) {
+  const int k = n - sg.first;
+  const int c1 = sg.c[1] + k * sg.d[1], c2 = sg.c[2] + k * sg.d[2], c3 = sg.c[3] + k * sg.d[3];
+  if (sg.rank4) {
+    ptx::tma_load_4d(dst, m, bar, 0, c1, c2, c3);
+    ptx::tma_load_4d(dst + HALF_BYTES, m, bar, 64, c1, c2, c3);
+  } else {
+    const int c4 = sg.c[4] + k * sg.d[4];
+    ptx::tma_load_5d(dst, m, bar, 0, c1, c2, c3, c4);
+    ptx::tma_load_5d(dst + HALF_BYTES, m, bar, 64, c1, c2, c3, c4);
+  }
+}
+
+// One entry of the CTA's item ring: everything any role needs to know about an item, worked out once
+// by the planner warp a few items ahead instead of by every warp at every item boundary (the index
+// arithmetic has divisions in it, and softmax warps have no issue slots to spare).
+constexpr int ITEM_RING = 4;
+struct ItemSlot {
+  int valid;                     // 0: end of this CTA's list
+  int n_kv;                      // key tiles of the item (> 0)
+  int b, h0, h1, hk;
+  // shared-key modes: what the TMA thread needs to request the tiles
+  int n_text;                    // tiles of the first key segment (== n_kv unless text + image keys)
+  int q0_text, q1_text, q0_rank4, q1_rank4;
+  KvSegment seg0, seg1;
+  int q0[5], q1[5];              // box coordinates of the two query sub-tiles
+  PairTile pt;                   // for the cp.async loaders (key slots -> tokens)
+  int token[2][TILE_M];          // per sub-tile and query row: token (-1: padding row) and its inclusive
+  int lo[2][TILE_M];             // interval of key slots
+  int hi[2][TILE_M];
+};
+__device__ __forceinline__ void plan_query(const Problem& prob, const Tile& t, int head, int batch, int c[5], int* is_text,
+                                           int* rank4) {
+  int start; bool text;
+  tma_q_start(t, &start, &text);
+  *is_text = tma_box_coords(prob, t, start, text, head, batch, c);
+  *rank4 = *is_text || t.kind == KIND_LLM_WINDOW;
+}
+// Planner warp: fills ring slot after ring slot with the CTA's non-empty items, then one end marker.
+// slot_ready[r] completes once per fill of slot r; slot_free[r] once all consumers have let go of it.
+__device__ __forceinline__ void plan_items(const DualParams& p, ItemSlot* ring, uint64_t* slot_ready, uint64_t* slot_free,
+                                           int cta, int n_cta, int lane, bool plan_boxes, volatile int* abort_p) {
+  int seq = 0;
+  for (int i = 0;; ++i) {
+    DualItem di;
+    bool valid = false;
+    for (;; ++seq) {
+      const int item = dual_item_index(seq, cta, n_cta);
+      if (item >= p.n_items) break;
+      di = dual_decode(p, item);
+      if (di.pt.kv.n_kv_tiles > 0) { valid = true; ++seq; break; }
+    }
+    const int r = i % ITEM_RING;
+    if (i >= ITEM_RING && !ptx::mbar_wait(&slot_free[r], ((i / ITEM_RING) - 1) & 1, abort_p)) {
+      if (*abort_p == 1) *abort_p = 51;
+      return;
+    }
+    ItemSlot& sl = ring[r];
+    if (valid) {
+#pragma unroll 1
+      for (int row = lane; row < TILE_M; row += 32) {
+#pragma unroll
+        for (int sx = 0; sx < 2; ++sx) {
+          int token, lo, hi;
+          pair_q_row(p.f.prob, di.pt, sx, row, &token, &lo, &hi);
+          sl.token[sx][row] = token;
+          sl.lo[sx][row] = lo;
+          sl.hi[sx][row] = hi;
+        }
+      }
+    }
+    if (lane == 0) {
+      sl.valid = valid;
+      if (valid) {
+        const int n_kv = di.pt.kv.n_kv_tiles;
+        sl.n_kv = n_kv;
+        sl.b = di.b; sl.h0 = di.h0; sl.h1 = di.h1; sl.hk = di.hk;
+        sl.pt = di.pt;
+        if (plan_boxes) {
+          const bool image_kind = di.pt.kv.kind == KIND_IMG_SCATTER;
+          const int n_text = image_kind && TEXT_LEN / TILE_N < n_kv ? TEXT_LEN / TILE_N : n_kv;
+          sl.n_text = n_text;
+          kv_segment(p.f.prob, di.pt.kv, 0, n_text, di.hk, di.b, &sl.seg0);
+          if (n_text < n_kv) kv_segment(p.f.prob, di.pt.kv, n_text, n_kv, di.hk, di.b, &sl.seg1);
+          // an absent sub-tile (odd tile count) is fed the other one's rows; its results are dropped
+          const Tile& t0 = di.pt.sub[0].n_kv_tiles > 0 ? di.pt.sub[0] : di.pt.sub[1];
+          const Tile& t1 = di.pt.sub[1].n_kv_tiles > 0 ? di.pt.sub[1] : di.pt.sub[0];
+          plan_query(p.f.prob, t0, di.h0, di.b, sl.q0, &sl.q0_text, &sl.q0_rank4);
+          plan_query(p.f.prob, t1, di.h1, di.b, sl.q1, &sl.q1_text, &sl.q1_rank4);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&slot_ready[r]);
+    if (!valid) return;
+  }
+}
+__device__ __forceinline__ void tma_fetch_box(const int c[5], int rank4, const CUtensorMap* m, uint32_t dst, uint64_t* bar) {
+  if (rank4) {
+    ptx::tma_load_4d(dst, m, bar, 0, c[1], c[2], c[3]);
+    ptx::tma_load_4d(dst + HALF_BYTES, m, bar, 64, c[1], c[2], c[3]);
+  } else {
+    ptx::tma_load_5d(dst, m, bar, 0, c[1], c[2], c[3], c[4]);
+    ptx::tma_load_5d(dst + HALF_BYTES, m, bar, 64, c[1], c[2], c[3], c[4]);
+  }
+}
+
 // Position in this CTA's stream of key tiles: item number `seq` of the CTA, key tile `n` of that item.
 struct TileCursor {
   int seq, n, n_kv;
@@ -215,7 +352,7 @@ __device__ __forceinline__ void cursor_next(const DualParams& p, TileCursor& c, 
 // Shared-memory layout and barriers the loaders of the split-K/V mode need.
 struct SplitLoaderCtx {
   uint32_t q_smem0, k_smem0, v_smem0;
-  uint64_t *q_full, *k_full, *v_full, *s0_full, *s1_full;
+  uint64_t *q_full, *q1_full, *k_full, *v_full, *s0_full, *s1_full;
   volatile int* abort_p;
 };
 
@@ -233,11 +370,12 @@ __device__ __forceinline__ void split_loader(const DualParams& p, const SplitLoa
 
   auto fetch_q = [&](const DualItem& di) {
     if (kTma) {
-      ptx::mbar_arrive_expect_tx(cx.q_full, 2 * TILE_BYTES);
+      ptx::mbar_arrive_expect_tx(cx.q_full, TILE_BYTES);
+      ptx::mbar_arrive_expect_tx(cx.q1_full, TILE_BYTES);
       const Tile& t0 = pair_kv_map(di.pt, 1, 0);
       const Tile& t1 = pair_kv_map(di.pt, 1, 1);
       tma_fetch_q(p.f.prob, t0, di.h0, di.b, q_op, cx.q_smem0, cx.q_full);
-      tma_fetch_q(p.f.prob, t1, di.h1, di.b, q_op, cx.q_smem0 + TILE_BYTES, cx.q_full);
+      tma_fetch_q(p.f.prob, t1, di.h1, di.b, q_op, cx.q_smem0 + TILE_BYTES, cx.q1_full);
     } else {
 #pragma unroll 1
       for (int sx = 0; sx < 2; ++sx) {
@@ -252,6 +390,7 @@ __device__ __forceinline__ void split_loader(const DualParams& p, const SplitLoa
         }
       }
       ptx::cp_async_mbar_arrive_noinc(cx.q_full);
+      ptx::cp_async_mbar_arrive_noinc(cx.q1_full);
     }
   };
   auto fetch_kv = [&](bool is_v, int sx, const TileCursor& c) {
@@ -308,8 +447,11 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
   extern __shared__ uint8_t smem_raw[];
   // barriers: 0 q_full, 1-2 k_full, 3-4 v_full, 5 s0_full, 6-7 s1_full[stage], 8-9 p_full[s],
   //           10-11 o_done[s], 12 drain, 13 xbar (softmax threads' exchange rendezvous),
-  //           14 l_ready (row sums of an item published), 15-16 o_free[s] (O of an item has been read)
-  __shared__ uint64_t bars[17];
+  //           14 l_ready (row sums of an item published), 15-16 o_free[s] (O of an item has been read),
+  //           17 q1_full (barrier 0 is Q0's)
+  //           18-21 slot_ready[r], 22-25 slot_free[r] (item ring)
+  __shared__ uint64_t bars[18 + 2 * ITEM_RING];
+  __shared__ ItemSlot ring[ITEM_RING];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
   __shared__ float xch_max[2][NSPLIT][TILE_M];      // [phase parity][column part][row]: partial row maxima
@@ -324,7 +466,8 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
   if (abort_flag != 0) return;                          // an earlier launch or CTA already failed
   __syncthreads();
 
-  uint64_t* q_full = &bars[0];
+  uint64_t* q_full = &bars[0];       // Q of sub-tile 0 has landed
+  uint64_t* q1_full = &bars[17];     // Q of sub-tile 1 has landed
   uint64_t* k_full = &bars[1];
   uint64_t* v_full = &bars[3];
   uint64_t* s0_full = &bars[5];     // QK0 of a key tile has completed
@@ -335,6 +478,8 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
   uint64_t* xbar = &bars[13];
   uint64_t* l_ready = &bars[14];
   uint64_t* o_free = &bars[15];
+  uint64_t* slot_ready = &bars[18];
+  uint64_t* slot_free = &bars[18 + ITEM_RING];
 
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem0 = smem_base;                                 // Q sub-tile s at + s * TILE_BYTES
@@ -345,6 +490,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     abort_flag = 0;
     const uint32_t producers = p.use_tma ? 1 : 128;       // one TMA-issuing thread, or every loader thread
     ptx::mbar_init(q_full, producers);
+    ptx::mbar_init(q1_full, producers);
     for (int j = 0; j < KV_STAGES; ++j) {
       ptx::mbar_init(&k_full[j], producers);
       ptx::mbar_init(&v_full[j], producers);
@@ -364,6 +510,13 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     ptx::mbar_init(l_ready, SM_WARPS);
     ptx::mbar_init(&o_free[0], p.use_tma ? 128 : SM_THREADS);   // whoever runs the epilogue
     ptx::mbar_init(&o_free[1], p.use_tma ? 128 : SM_THREADS);
+    // ring consumers, one arrival per warp: softmax warps, the MMA warp, epilogue warps or cp.async
+    // loader warps, and the TMA thread (the split-K/V loaders keep their own cursor)
+    const uint32_t consumers = SM_WARPS + 1 + (p.use_tma ? 4 + (kSplitKV ? 0 : 1) : (kSplitKV ? 0 : 4));
+    for (int r = 0; r < ITEM_RING; ++r) {
+      ptx::mbar_init(&slot_ready[r], 1);
+      ptx::mbar_init(&slot_free[r], consumers);
+    }
     ptx::fence_mbar_init();
   }
   if (warp == 0) {
@@ -386,6 +539,15 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     if (!ok) { if (*abort_p == 1) *abort_p = (code); }                              \
   } while (0)
 
+  // Item `seq` of this CTA's list, from the ring; leaves the loop at the end marker.
+#define INTRA_RING_ACQUIRE(sl, code)                                                 \
+  const ItemSlot& sl = ring[seq % ITEM_RING];                                        \
+  ok = ptx::mbar_wait(&slot_ready[seq % ITEM_RING], (seq / ITEM_RING) & 1, abort_p); \
+  if (!ok) { if (*abort_p == 1) *abort_p = (code); break; }                          \
+  if (!sl.valid) break
+#define INTRA_RING_RELEASE_WARP()                                                    \
+  do { __syncwarp(); if (lane == 0) ptx::mbar_arrive(&slot_free[seq % ITEM_RING]); } while (0)
+
   if (warp < SM_WARPS) {
     // ================================ softmax / correction / epilogue ==========================
     // All softmax warps work on ONE sub-tile at a time, alternating between the two: thread (part, row)
@@ -403,14 +565,12 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     bool ok = true;
 
     for (int seq = 0; ok; ++seq) {
-      const int item = dual_item_index(seq, cta, n_cta);
-      if (item >= p.n_items) break;
-      const DualItem di = dual_decode(p, item);
-      const int n_kv = di.pt.kv.n_kv_tiles;
-      if (n_kv == 0) continue;
-      int token[2], lo[2], hi[2];
-      pair_q_row(p.f.prob, di.pt, 0, row, &token[0], &lo[0], &hi[0]);
-      pair_q_row(p.f.prob, di.pt, 1, row, &token[1], &lo[1], &hi[1]);
+      INTRA_RING_ACQUIRE(sl, 52);
+      const int n_kv = sl.n_kv;
+      const int lo[2] = {sl.lo[0][row], sl.lo[1][row]}, hi[2] = {sl.hi[0][row], sl.hi[1][row]};
+      const int token[2] = {sl.token[0][row], sl.token[1][row]};
+      const int item_b = sl.b, item_h[2] = {sl.h0, sl.h1};
+      INTRA_RING_RELEASE_WARP();
       INTRA_TRACE_ITEM(tid == 0, 1, 0);
       float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};    // running maxima (identical in both halves)
       float l_part[2] = {0.f, 0.f};                       // this half's share of the row sums
@@ -527,9 +687,9 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
 #pragma unroll
         for (int o = 1; o < NSPLIT; ++o) l_tot += xch_sum[ipar][sx][(half + o) % NSPLIT][row];
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-        const int h = sx ? di.h1 : di.h0;
+        const int h = item_h[sx];
         const int tk = token[sx];
-        __nv_bfloat16* dst = p.f.o + di.b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh + half * COLS;
+        __nv_bfloat16* dst = p.f.o + item_b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh + half * COLS;
         store_o_row(lane_addr + 256 + sx * 128 + half * COLS, COLS, inv, dst, tk >= 0, p.wide_stores != 0);
         ptx::tc_fence_before();
         ptx::mbar_arrive(&o_free[sx]);
@@ -552,70 +712,68 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       const int row = tid & 127;
       const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
       for (int seq = 0; ok; ++seq) {
-        const int item = dual_item_index(seq, cta, n_cta);
-        if (item >= p.n_items) break;
-        const DualItem di = dual_decode(p, item);
-        if (di.pt.kv.n_kv_tiles == 0) continue;
-        int token[2], lo, hi;
-        pair_q_row(p.f.prob, di.pt, 0, row, &token[0], &lo, &hi);
-        pair_q_row(p.f.prob, di.pt, 1, row, &token[1], &lo, &hi);
+        INTRA_RING_ACQUIRE(sl, 53);
+        const int token[2] = {sl.token[0][row], sl.token[1][row]};
+        const int item_b = sl.b, item_h[2] = {sl.h0, sl.h1};
+        INTRA_RING_RELEASE_WARP();
         const int ipar = n_done & 1;
         ok = ptx::mbar_wait(l_ready, ipar, abort_p);
         if (!ok) { if (*abort_p == 1) *abort_p = 41; break; }
+        INTRA_TRACE_ITEM(lt == 0, 2, 0);
 #pragma unroll
         for (int sx = 0; sx < 2; ++sx) {
           ok = ptx::mbar_wait(&o_done[sx], ipar, abort_p);         // last PV of this item
           if (!ok) { if (*abort_p == 1) *abort_p = 42 + sx; break; }
           ptx::tc_fence_after();
+          INTRA_TRACE_ITEM(lt == 0, 2, 1 + 2 * sx);
           float l_tot = 0.f;
 #pragma unroll
           for (int o = 0; o < NSPLIT; ++o) l_tot += xch_sum[ipar][sx][o][row];
           const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-          const int h = sx ? di.h1 : di.h0;
+          const int h = item_h[sx];
           const int tk = token[sx];
-          __nv_bfloat16* dst = p.f.o + di.b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh;
+          __nv_bfloat16* dst = p.f.o + item_b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh;
           store_o_row(lane_addr + 256 + sx * 128, 128, inv, dst, tk >= 0, p.wide_stores != 0);
           ptx::tc_fence_before();
           ptx::mbar_arrive(&o_free[sx]);                           // the next item's first PV may overwrite O
+          INTRA_TRACE_ITEM(lt == 0, 2, 2 + 2 * sx);
         }
         ++n_done;
       }
     } else if (kSplitKV) {
-      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, k_full, v_full, s0_full, s1_full, abort_p};
+      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, q1_full, k_full, v_full, s0_full, s1_full, abort_p};
       split_loader<false>(p, cx, cta, n_cta, lt);
     } else {
       // ---- cp.async row gathers by all 128 loader threads (ragged shapes) ------------------------
       const int chunk = lt & 15;                          // 16-byte chunk of the 256-byte row
       const int rsub = lt >> 4;                           // row within a pass of 8 rows
       for (int seq = 0; ok; ++seq) {
-        const int item = dual_item_index(seq, cta, n_cta);
-        if (item >= p.n_items) break;
-        const DualItem di = dual_decode(p, item);
-        const int n_kv = di.pt.kv.n_kv_tiles;
-        if (n_kv == 0) continue;
+        INTRA_RING_ACQUIRE(sl, 54);
+        const int n_kv = sl.n_kv;
         if (n_done > 0) {
           INTRA_WAIT_TILE_DONE(kc - 1, 21);
           if (!ok) break;
         }
         {
-          const __nv_bfloat16* qb0 = p.f.q + di.b * p.f.qs.sb + di.h0 * p.f.qs.sh + chunk * 8;
-          const __nv_bfloat16* qb1 = p.f.q + di.b * p.f.qs.sb + di.h1 * p.f.qs.sh + chunk * 8;
+          const __nv_bfloat16* qb0 = p.f.q + sl.b * p.f.qs.sb + sl.h0 * p.f.qs.sh + chunk * 8;
+          const __nv_bfloat16* qb1 = p.f.q + sl.b * p.f.qs.sb + sl.h1 * p.f.qs.sh + chunk * 8;
 #pragma unroll 4
           for (int ps = 0; ps < TILE_M / 8; ++ps) {
             const int row = ps * 8 + rsub;
-            int token, lo, hi;
-            pair_q_row(p.f.prob, di.pt, 0, row, &token, &lo, &hi);
+            int token = sl.token[0][row];
             const void* src = token >= 0 ? static_cast<const void*>(qb0 + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
             ptx::cp_async_16(q_smem0 + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
-            if (p.row_pairs) pair_q_row(p.f.prob, di.pt, 1, row, &token, &lo, &hi);
+            token = sl.token[1][row];
             src = token >= 0 ? static_cast<const void*>(qb1 + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
             ptx::cp_async_16(q_smem0 + TILE_BYTES + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
           }
           ptx::cp_async_mbar_arrive_noinc(q_full);
+          ptx::cp_async_mbar_arrive_noinc(q1_full);
         }
-        const __nv_bfloat16* kb = p.f.k + di.b * p.f.ks.sb + di.hk * p.f.ks.sh + chunk * 8;
-        const __nv_bfloat16* vb = p.f.v + di.b * p.f.vs.sb + di.hk * p.f.vs.sh + chunk * 8;
-        const Tile kv = di.pt.kv;
+        const __nv_bfloat16* kb = p.f.k + sl.b * p.f.ks.sb + sl.hk * p.f.ks.sh + chunk * 8;
+        const __nv_bfloat16* vb = p.f.v + sl.b * p.f.vs.sb + sl.hk * p.f.vs.sh + chunk * 8;
+        const Tile kv = sl.pt.kv;
+        INTRA_RING_RELEASE_WARP();
         for (int n = 0; n < n_kv && ok; ++n, ++kc) {
           const int stage = kc % KV_STAGES;
           int tokens[TILE_N / 8];
@@ -657,7 +815,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     // ================================ MMA issue ==================================================
     ptx::setmaxnreg_dec<MMA_REGS>();
     if (kSplitKV && warp == SM_WARPS + 5 && p.use_tma && lane == 0) {
-      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, k_full, v_full, s0_full, s1_full, abort_p};
+      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, q1_full, k_full, v_full, s0_full, s1_full, abort_p};
       split_loader<true>(p, cx, cta, n_cta, 0);
     } else if (warp == SM_WARPS + 5 && p.use_tma && lane == 0) {
       // ---- one thread drives the TMA unit ------------------------------------------------------------
@@ -670,46 +828,55 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       const TmaOperand q_op = {&p.maps.q_main, &p.maps.q_text, &p.maps.q_main};
       const TmaOperand k_op = {&p.maps.k_main, &p.maps.k_text, &p.maps.k_aux};
       const TmaOperand v_op = {&p.maps.v_main, &p.maps.v_text, &p.maps.v_aux};
+      const CUtensorMap* k_main = p.f.prob.kind == KIND_IMG_GATHER0 ? k_op.aux_map : k_op.main_map;
+      const CUtensorMap* v_main = p.f.prob.kind == KIND_IMG_GATHER0 ? v_op.aux_map : v_op.main_map;
       for (int seq = 0; ok; ++seq) {
-        const int item = dual_item_index(seq, cta, n_cta);
-        if (item >= p.n_items) break;
-        const DualItem di = dual_decode(p, item);
-        const int n_kv = di.pt.kv.n_kv_tiles;
-        if (n_kv == 0) continue;
-        if (n_done > 0) {                               // Q buffers: last QK^T of the previous item
-          INTRA_WAIT_TILE_DONE(kc - 1, 21);
-          if (!ok) break;
-        }
-        INTRA_TRACE_ITEM(true, 3, 0);
-        ptx::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
-        {
-          // an absent sub-tile (odd tile count) is fed the other one's rows; its results are dropped
-          const Tile& t0 = di.pt.sub[0].n_kv_tiles > 0 ? di.pt.sub[0] : di.pt.sub[1];
-          const Tile& t1 = di.pt.sub[1].n_kv_tiles > 0 ? di.pt.sub[1] : di.pt.sub[0];
-          tma_fetch_q(p.f.prob, t0, di.h0, di.b, q_op, q_smem0, q_full);
-          tma_fetch_q(p.f.prob, t1, di.h1, di.b, q_op, q_smem0 + TILE_BYTES, q_full);
-        }
+        INTRA_RING_ACQUIRE(sl, 55);
+        const int n_kv = sl.n_kv, n_text = sl.n_text;
         for (int n = 0; n < n_kv && ok; ++n, ++kc) {
           const int stage = kc % KV_STAGES;
+          const KvSegment& sg = n < n_text ? sl.seg0 : sl.seg1;
+          const CUtensorMap* kmap = sg.text ? k_op.text_map : k_main;
+          const CUtensorMap* vmap = sg.text ? v_op.text_map : v_main;
           if (kc >= 2) {                                // K stage: QK1 of key tile kc-2
             INTRA_WAIT_TILE_DONE(kc - 2, 22);
             if (!ok) break;
           }
           INTRA_TRACE_EV(true, 3, n, 0);
           ptx::mbar_arrive_expect_tx(&k_full[stage], TILE_BYTES);
-          tma_fetch_kv(p.f.prob, di.pt.kv, n, di.hk, di.b, k_op, k_smem0 + stage * TILE_BYTES, &k_full[stage]);
+          tma_fetch_planned(sg, n, kmap, k_smem0 + stage * TILE_BYTES, &k_full[stage]);
           INTRA_TRACE_EV(true, 3, n, 1);
-          if (kc >= 2) {                                // V stage: PV1 of key tile kc-2, issued before QK1 of kc-1
+          if (n == 0) {
+            // The item's queries go in between its first K and V tiles, each as early as its buffer
+            // frees: Q0 after QK0 of the previous item's last key tile, Q1 after that tile's QK1.
+            if (n_done > 0) {
+              ok = ptx::mbar_wait(s0_full, (kc - 1) & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 21; break; }
+            }
+            INTRA_TRACE_ITEM(true, 3, 0);
+            ptx::mbar_arrive_expect_tx(q_full, TILE_BYTES);
+            tma_fetch_box(sl.q0, sl.q0_rank4, sl.q0_text ? q_op.text_map : q_op.main_map, q_smem0, q_full);
+          }
+          if (kc >= 2 || (n == 0 && n_done > 0)) {      // V stage: PV1 of key tile kc-2, issued before QK1 of kc-1
             INTRA_WAIT_TILE_DONE(kc - 1, 23);
             if (!ok) break;
           }
+          if (n == 0) {
+            ptx::mbar_arrive_expect_tx(q1_full, TILE_BYTES);
+            tma_fetch_box(sl.q1, sl.q1_rank4, sl.q1_text ? q_op.text_map : q_op.main_map, q_smem0 + TILE_BYTES, q1_full);
+          }
           INTRA_TRACE_EV(true, 3, n, 2);
           ptx::mbar_arrive_expect_tx(&v_full[stage], TILE_BYTES);
-          tma_fetch_kv(p.f.prob, di.pt.kv, n, di.hk, di.b, v_op, v_smem0 + stage * TILE_BYTES, &v_full[stage]);
+          tma_fetch_planned(sg, n, vmap, v_smem0 + stage * TILE_BYTES, &v_full[stage]);
           INTRA_TRACE_EV(true, 3, n, 3);
         }
+        if (!ok) break;
+        ptx::mbar_arrive(&slot_free[seq % ITEM_RING]);
         ++n_done;
       }
+    } else if (warp == SM_WARPS + 6) {
+      // ---- planner: keeps the item ring filled -------------------------------------------------------
+      plan_items(p, ring, slot_ready, slot_free, cta, n_cta, lane, p.use_tma && !kSplitKV, abort_p);
     }
     if (warp == SM_WARPS + 4) {
       uint32_t kc = 0;                                    // key tiles issued so far
@@ -725,11 +892,9 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       bool ok = true;
 
       for (int seq = 0; ok; ++seq) {
-        const int item = dual_item_index(seq, cta, n_cta);
-        if (item >= p.n_items) break;
-        const DualItem di = dual_decode(p, item);
-        const int n_kv = di.pt.kv.n_kv_tiles;
-        if (n_kv == 0) continue;
+        INTRA_RING_ACQUIRE(sl, 56);
+        const int n_kv = sl.n_kv;
+        INTRA_RING_RELEASE_WARP();
         INTRA_TRACE_ITEM(lane == 0, 0, 0);
         ok = ptx::mbar_wait(q_full, n_done & 1, abort_p);
         if (!ok) { if (*abort_p == 1) *abort_p = 31; break; }
@@ -770,6 +935,12 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             __syncwarp();
             ++it1;
             pend = false;
+          }
+          if (n == 0) {                                   // the item's second query tile
+            ok = ptx::mbar_wait(q1_full, n_done & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 42; break; }
+            ptx::fence_proxy_async_smem();
+            ptx::tc_fence_after();
           }
           if (kSplitKV) {                                 // sub-tile 1's own K buffer
             ok = ptx::mbar_wait(&k_full[1], par, abort_p);
@@ -841,6 +1012,8 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     }
   }
 #undef INTRA_WAIT_TILE_DONE
+#undef INTRA_RING_ACQUIRE
+#undef INTRA_RING_RELEASE_WARP
 
   // ---- teardown --------------------------------------------------------------------------------
   ptx::tc_fence_before();
