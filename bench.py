@@ -149,7 +149,7 @@ class ClockSampler:
                 self.samples.append(self._sample_nvml() if self._nvml else self._sample_smi())
             except Exception:
                 pass
-            self._stop.wait(0.02 if self._nvml else 0.2)
+            self._stop.wait(0.005 if self._nvml else 0.2)
 
     def __enter__(self):
         self._thread = threading.Thread(target=self._run, daemon=True)

@@ -56,9 +56,14 @@ struct DualCfg {
   static constexpr int SM_WARPS = 4 * NSPLIT;             // softmax warps
   static constexpr int SM_THREADS = 128 * NSPLIT;
   static constexpr int THREADS = SM_THREADS + 256;        // + epilogue / loader warpgroup + MMA / TMA warpgroup
-  static constexpr int SM_REGS = NSPLIT == 2 ? 192 : 88;  // setmaxnreg budgets: softmax, epilogue / loaders, MMA / TMA
+  // setmaxnreg budgets: softmax, epilogue / loaders, MMA / TMA / planner. The last group must not spill:
+  // a local-memory access in the MMA-issuing thread's loop stalls the tensor pipe. Sums: 512 threads
+  // start with 128 registers each (65536), 768 threads with 80 (61440).
+  static constexpr int SM_REGS = NSPLIT == 2 ? 176 : 88;
   static constexpr int EP_REGS = 64;
-  static constexpr int MMA_REGS = NSPLIT == 2 ? 64 : 48;
+  static constexpr int MMA_REGS = NSPLIT == 2 ? 96 : 64;
+  static_assert(SM_THREADS * SM_REGS + 128 * (EP_REGS + MMA_REGS) <= (NSPLIT == 2 ? 65536 : 61440),
+                "register budgets exceed what the CTA was launched with: setmaxnreg.inc would never return");
 };
 constexpr int KV_STAGES = 2;
 constexpr int DUAL_SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + 1024;   // Q0 Q1 | K ring | V ring

@@ -324,7 +324,11 @@ INTRA_HD PairTile make_pair(const Problem& p, int row_pairs, int idx) {
       if (2 * idx + 1 < p.n_tiles) idx_first = 2 * idx + 1;
       break;
     case KIND_IMG_SCATTER: {
-      const int g = idx % IMG_GROUPS, mp = idx / IMG_GROUPS;
+      // All pairs weigh the same, so the order is free: group-major, so that the pairs in flight at any
+      // moment are the row pairs of a few (head, group) key sets that stay in L2, instead of one row
+      // pair of every group, which re-reads every key set from DRAM once per row pair.
+      const int n_mp = ceil_div(p.tiles_m, 2);
+      const int g = idx / n_mp, mp = idx % n_mp;
       idx_first = (2 * mp) * IMG_GROUPS + g;
       if (2 * mp + 1 < p.tiles_m) idx_second = (2 * mp + 1) * IMG_GROUPS + g;
       break;
