@@ -332,32 +332,12 @@ __device__ __forceinline__ void tma_fetch_box(const int c[5], int rank4, const C
   }
 }
 
-// Position in this CTA's stream of key tiles: item number `seq` of the CTA, key tile `n` of that item.
-struct TileCursor {
-  int seq, n, n_kv;
-  bool valid;
-  DualItem di;
-};
-// Move to the first non-empty item at or after c.seq.
-__device__ __forceinline__ void cursor_seek(const DualParams& p, TileCursor& c, int cta, int n_cta) {
-  for (;; ++c.seq) {
-    const int item = dual_item_index(c.seq, cta, n_cta);
-    if (item >= p.n_items) { c.valid = false; return; }
-    c.di = dual_decode(p, item);
-    c.n_kv = c.di.pt.kv.n_kv_tiles;
-    if (c.n_kv > 0) { c.n = 0; c.valid = true; return; }
-  }
-}
-__device__ __forceinline__ void cursor_next(const DualParams& p, TileCursor& c, int cta, int n_cta) {
-  if (++c.n < c.n_kv) return;
-  ++c.seq;
-  cursor_seek(p, c, cta, n_cta);
-}
-
 // Shared-memory layout and barriers the loaders of the split-K/V mode need.
 struct SplitLoaderCtx {
   uint32_t q_smem0, k_smem0, v_smem0;
   uint64_t *q_full, *q1_full, *k_full, *v_full, *s0_full, *s1_full;
+  const ItemSlot* ring;
+  uint64_t *slot_ready, *slot_free;
   volatile int* abort_p;
 };
 
@@ -367,29 +347,26 @@ struct SplitLoaderCtx {
 // are requested; likewise for sub-tile 1, whose event also frees the Q buffers at an item's end.
 // kTma: one thread issues TMA boxes; otherwise all 128 loader threads gather rows with cp.async.
 template <bool kTma>
-__device__ __forceinline__ void split_loader(const DualParams& p, const SplitLoaderCtx& cx, int cta, int n_cta, int lt) {
+__device__ __forceinline__ void split_loader(const DualParams& p, const SplitLoaderCtx& cx, int lt) {
   const int chunk = lt & 15, rsub = lt >> 4;
   const TmaOperand q_op = {&p.maps.q_main, &p.maps.q_text, &p.maps.q_main};
   const TmaOperand k_op = {&p.maps.k_main, &p.maps.k_text, &p.maps.k_aux};
   const TmaOperand v_op = {&p.maps.v_main, &p.maps.v_text, &p.maps.v_aux};
 
-  auto fetch_q = [&](const DualItem& di) {
+  auto fetch_q = [&](const ItemSlot& sl) {
     if (kTma) {
       ptx::mbar_arrive_expect_tx(cx.q_full, TILE_BYTES);
       ptx::mbar_arrive_expect_tx(cx.q1_full, TILE_BYTES);
-      const Tile& t0 = pair_kv_map(di.pt, 1, 0);
-      const Tile& t1 = pair_kv_map(di.pt, 1, 1);
-      tma_fetch_q(p.f.prob, t0, di.h0, di.b, q_op, cx.q_smem0, cx.q_full);
-      tma_fetch_q(p.f.prob, t1, di.h1, di.b, q_op, cx.q_smem0 + TILE_BYTES, cx.q1_full);
+      tma_fetch_q(p.f.prob, pair_kv_map(sl.pt, 1, 0), sl.h0, sl.b, q_op, cx.q_smem0, cx.q_full);
+      tma_fetch_q(p.f.prob, pair_kv_map(sl.pt, 1, 1), sl.h1, sl.b, q_op, cx.q_smem0 + TILE_BYTES, cx.q1_full);
     } else {
 #pragma unroll 1
       for (int sx = 0; sx < 2; ++sx) {
-        const __nv_bfloat16* qb = p.f.q + di.b * p.f.qs.sb + (sx ? di.h1 : di.h0) * p.f.qs.sh + chunk * 8;
+        const __nv_bfloat16* qb = p.f.q + sl.b * p.f.qs.sb + (sx ? sl.h1 : sl.h0) * p.f.qs.sh + chunk * 8;
 #pragma unroll 4
         for (int ps = 0; ps < TILE_M / 8; ++ps) {
           const int row = ps * 8 + rsub;
-          int token, lo, hi;
-          pair_q_row(p.f.prob, di.pt, sx, row, &token, &lo, &hi);
+          const int token = sl.token[sx][row];
           const void* src = token >= 0 ? static_cast<const void*>(qb + int64_t(token) * p.f.qs.ss) : static_cast<const void*>(p.f.q);
           ptx::cp_async_16(cx.q_smem0 + sx * TILE_BYTES + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
         }
@@ -398,48 +375,63 @@ __device__ __forceinline__ void split_loader(const DualParams& p, const SplitLoa
       ptx::cp_async_mbar_arrive_noinc(cx.q1_full);
     }
   };
-  auto fetch_kv = [&](bool is_v, int sx, const TileCursor& c) {
-    const Tile& map = pair_kv_map(c.di.pt, 1, sx);
+  auto fetch_kv = [&](bool is_v, int sx, const ItemSlot& sl, int n) {
+    const Tile& map = pair_kv_map(sl.pt, 1, sx);
     const uint32_t dst = (is_v ? cx.v_smem0 : cx.k_smem0) + sx * TILE_BYTES;
     uint64_t* bar = is_v ? &cx.v_full[sx] : &cx.k_full[sx];
     if (kTma) {
       ptx::mbar_arrive_expect_tx(bar, TILE_BYTES);
-      tma_fetch_kv(p.f.prob, map, c.n, c.di.hk, c.di.b, is_v ? v_op : k_op, dst, bar);
+      tma_fetch_kv(p.f.prob, map, n, sl.hk, sl.b, is_v ? v_op : k_op, dst, bar);
     } else {
-      const __nv_bfloat16* base = is_v ? p.f.v + c.di.b * p.f.vs.sb + c.di.hk * p.f.vs.sh + chunk * 8
-                                       : p.f.k + c.di.b * p.f.ks.sb + c.di.hk * p.f.ks.sh + chunk * 8;
+      const __nv_bfloat16* base = is_v ? p.f.v + sl.b * p.f.vs.sb + sl.hk * p.f.vs.sh + chunk * 8
+                                       : p.f.k + sl.b * p.f.ks.sb + sl.hk * p.f.ks.sh + chunk * 8;
       const int64_t ss = is_v ? p.f.vs.ss : p.f.ks.ss;
 #pragma unroll 4
       for (int ps = 0; ps < TILE_N / 8; ++ps) {
         const int row = ps * 8 + rsub;
-        const int token = key_token(p.f.prob, map, c.n * TILE_N + row);
+        const int token = key_token(p.f.prob, map, n * TILE_N + row);
         const void* src = token >= 0 ? static_cast<const void*>(base + int64_t(token) * ss) : static_cast<const void*>(p.f.k);
         ptx::cp_async_16(dst + tile_offset(row, chunk), src, token >= 0 ? 16u : 0u);
       }
       ptx::cp_async_mbar_arrive_noinc(bar);
     }
   };
+  // one arrival per consumer warp; the TMA loader is a single thread
+  auto release = [&](int seq) {
+    if (kTma) { ptx::mbar_arrive(&cx.slot_free[seq % ITEM_RING]); return; }
+    __syncwarp();
+    if ((lt & 31) == 0) ptx::mbar_arrive(&cx.slot_free[seq % ITEM_RING]);
+  };
+  auto acquire = [&](int seq) -> const ItemSlot* {
+    if (!ptx::mbar_wait(&cx.slot_ready[seq % ITEM_RING], (seq / ITEM_RING) & 1, cx.abort_p)) {
+      if (*cx.abort_p == 1) *cx.abort_p = 57;
+      return nullptr;
+    }
+    const ItemSlot* sl = &cx.ring[seq % ITEM_RING];
+    return sl->valid ? sl : nullptr;
+  };
 
-  TileCursor cur;
-  cur.seq = 0;
-  cursor_seek(p, cur, cta, n_cta);
-  if (!cur.valid) return;
-  fetch_q(cur.di);
-  fetch_kv(false, 0, cur);
-  fetch_kv(false, 1, cur);
+  int seq = 0, n = 0;                                      // the key tile being fed: tile n of item seq
+  const ItemSlot* cur = acquire(0);
+  if (cur == nullptr) { if (!kTma) { ptx::cp_async_commit(); ptx::cp_async_wait<0>(); } return; }
+  fetch_q(*cur);
+  fetch_kv(false, 0, *cur, 0);
+  fetch_kv(false, 1, *cur, 0);
   for (uint32_t j = 0;; ++j) {                            // j: key tiles of this CTA so far
-    TileCursor nxt = cur;
-    cursor_next(p, nxt, cta, n_cta);
-    const bool new_item = nxt.valid && nxt.n == 0;
+    const bool last_of_item = n + 1 >= cur->n_kv;
+    const ItemSlot* nxt = last_of_item ? acquire(seq + 1) : cur;     // nullptr: the list ends (or a wait gave up)
+    const int nn = last_of_item ? 0 : n + 1;
     if (!ptx::mbar_wait(cx.s0_full, j & 1, cx.abort_p)) { if (*cx.abort_p == 1) *cx.abort_p = 24; break; }
-    fetch_kv(true, 0, cur);
-    if (nxt.valid) fetch_kv(false, 0, nxt);
+    fetch_kv(true, 0, *cur, n);
+    if (nxt != nullptr) fetch_kv(false, 0, *nxt, nn);
     if (!ptx::mbar_wait(&cx.s1_full[j & 1], (j >> 1) & 1, cx.abort_p)) { if (*cx.abort_p == 1) *cx.abort_p = 25; break; }
-    fetch_kv(true, 1, cur);
-    if (!nxt.valid) break;
-    if (new_item) fetch_q(nxt.di);
-    fetch_kv(false, 1, nxt);
+    fetch_kv(true, 1, *cur, n);
+    if (nxt == nullptr) break;
+    if (last_of_item) fetch_q(*nxt);
+    fetch_kv(false, 1, *nxt, nn);
+    if (last_of_item) { release(seq); ++seq; }
     cur = nxt;
+    n = nn;
   }
   if (!kTma) { ptx::cp_async_commit(); ptx::cp_async_wait<0>(); }
 }
@@ -515,9 +507,9 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     ptx::mbar_init(l_ready, SM_WARPS);
     ptx::mbar_init(&o_free[0], p.use_tma ? 128 : SM_THREADS);   // whoever runs the epilogue
     ptx::mbar_init(&o_free[1], p.use_tma ? 128 : SM_THREADS);
-    // ring consumers, one arrival per warp: softmax warps, the MMA warp, epilogue warps or cp.async
-    // loader warps, and the TMA thread (the split-K/V loaders keep their own cursor)
-    const uint32_t consumers = SM_WARPS + 1 + (p.use_tma ? 4 + (kSplitKV ? 0 : 1) : (kSplitKV ? 0 : 4));
+    // ring consumers, one arrival per warp: softmax warps, the MMA warp, and either the four epilogue warps
+    // plus the TMA thread, or the four cp.async loader warps
+    const uint32_t consumers = SM_WARPS + 1 + (p.use_tma ? 5 : 4);
     for (int r = 0; r < ITEM_RING; ++r) {
       ptx::mbar_init(&slot_ready[r], 1);
       ptx::mbar_init(&slot_free[r], consumers);
@@ -746,8 +738,9 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
         ++n_done;
       }
     } else if (kSplitKV) {
-      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, q1_full, k_full, v_full, s0_full, s1_full, abort_p};
-      split_loader<false>(p, cx, cta, n_cta, lt);
+      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, q1_full, k_full, v_full, s0_full, s1_full,
+                                 ring, slot_ready, slot_free, abort_p};
+      split_loader<false>(p, cx, lt);
     } else {
       // ---- cp.async row gathers by all 128 loader threads (ragged shapes) ------------------------
       const int chunk = lt & 15;                          // 16-byte chunk of the 256-byte row
@@ -820,8 +813,9 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     // ================================ MMA issue ==================================================
     ptx::setmaxnreg_dec<MMA_REGS>();
     if (kSplitKV && warp == SM_WARPS + 5 && p.use_tma && lane == 0) {
-      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, q1_full, k_full, v_full, s0_full, s1_full, abort_p};
-      split_loader<true>(p, cx, cta, n_cta, 0);
+      const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, q1_full, k_full, v_full, s0_full, s1_full,
+                                 ring, slot_ready, slot_free, abort_p};
+      split_loader<true>(p, cx, 0);
     } else if (warp == SM_WARPS + 5 && p.use_tma && lane == 0) {
       // ---- one thread drives the TMA unit ------------------------------------------------------------
       uint32_t kc = 0;                                    // K / V tiles requested so far (ring position)
