@@ -55,6 +55,25 @@ int intra_b200_fwd_image(const void* q, const void* k, const void* v, void* out,
                          int pattern, int width, float softmax_scale,
                          int device, void* cuda_stream);
 
+/* The two functions above with one more output: lse, (B, H, S) fp32 contiguous, lse[b][h][i] = the
+ * natural log of sum_j exp(softmax_scale * q_i . k_j) over the keys j token i attends. It is what merging
+ * partial attention results over disjoint key sets needs (split KV, ring attention). The reference's
+ * bindings return this tensor as `softmax_lse` (csrc/flash_attn/flash_api.cpp:470, 551, 670) although its
+ * INTRA kernels compute it and then drop it (csrc/flash_attn/src/flash_fwd_kernel.h:5675); here it is
+ * written. `lse` must be 4-byte aligned device memory; every element is written. */
+int intra_b200_fwd_llm_lse(const void* q, const void* k, const void* v, void* out, float* lse,
+                           int B, int S, int H, int Hkv,
+                           const int64_t q_strides[3], const int64_t k_strides[3],
+                           const int64_t v_strides[3], const int64_t out_strides[3],
+                           int pattern, int group_num, int window, float softmax_scale,
+                           int device, void* cuda_stream);
+int intra_b200_fwd_image_lse(const void* q, const void* k, const void* v, void* out, float* lse,
+                             int B, int S, int H,
+                             const int64_t q_strides[3], const int64_t k_strides[3],
+                             const int64_t v_strides[3], const int64_t out_strides[3],
+                             int pattern, int width, float softmax_scale,
+                             int device, void* cuda_stream);
+
 /* Text for a status code; replaces the reference's TORCH_CHECK messages
  * (csrc/flash_attn/flash_api.cpp:377-394, 576-597). */
 const char* intra_b200_strerror(int status);

@@ -23,6 +23,10 @@ SIGNATURES = {
                                 _i, _i, _i, _f, _i, _vp]),
     "intra_b200_fwd_image": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _I64x3, _I64x3, _I64x3, _I64x3,
                                   _i, _i, _f, _i, _vp]),
+    "intra_b200_fwd_llm_lse": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _I64x3, _I64x3, _I64x3, _I64x3,
+                                    _i, _i, _i, _f, _i, _vp]),
+    "intra_b200_fwd_image_lse": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _I64x3, _I64x3, _I64x3, _I64x3,
+                                      _i, _i, _f, _i, _vp]),
     "intra_b200_fwd_llm_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _I64x3, _I64x3, _I64x3, _I64x3,
                                         _i, _i, _i, _f, _i, _vp, ctypes.POINTER(_i)]),
     "intra_b200_strerror": (ctypes.c_char_p, [_i]),

@@ -58,7 +58,16 @@ struct FwdParams {
   Problem prob;
   float scale_log2;      // softmax_scale * log2(e)
   int* status;           // device word: 0 = ok
+  float* lse;            // optional (B, H, S) fp32: natural log of each row's softmax denominator; null = not wanted
 };
+
+// log(sum_j exp(scale * s_j)) of a row from the running maximum its probabilities were taken against
+// (in raw score units, possibly stale: the lazy rescale keeps p = 2^(s * scale_log2 - m * scale_log2)
+// consistent with it) and their sum. The reference computes the same quantity and drops it
+// (csrc/flash_attn/src/flash_fwd_kernel.h:5675).
+__device__ __forceinline__ float row_lse(float m_run, float l_sum, float scale_log2) {
+  return l_sum > 0.f ? (m_run * scale_log2 + log2f(l_sum)) * 0.6931471805599453f : -CUDART_INF_F;
+}
 
 // Byte offset of 16-byte chunk `chunk` (0..15) of row `row` inside a swizzled tile: two 64-element
 // halves, 128-byte rows, chunk index xor-ed with (row mod 8) as the 128-byte swizzle prescribes.
@@ -247,6 +256,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) intra_fwd_kernel(const FwdPara
     if (ok) {
       ptx::tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      if (p.lse != nullptr && token >= 0) p.lse[(int64_t(b) * p.H + h) * p.prob.S + token] = row_lse(m_run, l_run, p.scale_log2);
       __nv_bfloat16* dst = p.o + b * p.os.sb + int64_t(token < 0 ? 0 : token) * p.os.ss + h * p.os.sh;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {

@@ -36,8 +36,11 @@ namespace intra {
 #ifdef INTRA_TRACE
 __device__ long long g_trace[4 * 64 * 8];
 __device__ long long g_trace_item[4 * 32 * 8];
+#ifndef INTRA_TRACE_SEQ
+#define INTRA_TRACE_SEQ 0
+#endif
 #define INTRA_TRACE_EV(cond, role, iter, ev) \
-  do { if ((cond) && blockIdx.x == 0 && seq == 0 && (iter) < 64) g_trace[((role) * 64 + (iter)) * 8 + (ev)] = clock64(); } while (0)
+  do { if ((cond) && blockIdx.x == 0 && seq == INTRA_TRACE_SEQ && (iter) < 64) g_trace[((role) * 64 + (iter)) * 8 + (ev)] = clock64(); } while (0)
 #define INTRA_TRACE_ITEM(cond, role, ev) \
   do { if ((cond) && blockIdx.x == 0 && seq < 32) g_trace_item[((role) * 32 + seq) * 8 + (ev)] = clock64(); } while (0)
 #else
@@ -453,6 +456,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
   __shared__ int abort_flag;
   __shared__ float xch_max[2][NSPLIT][TILE_M];      // [phase parity][column part][row]: partial row maxima
   __shared__ float xch_sum[2][2][NSPLIT][TILE_M];   // [item parity][sub-tile][column part][row]: partial row sums
+  __shared__ float xch_m[2][2][TILE_M];             // [item parity][sub-tile][row]: the running maximum they refer to
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -661,6 +665,10 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       const int ipar = n_done & 1;
       xch_sum[ipar][0][half][row] = l_part[0];
       xch_sum[ipar][1][half][row] = l_part[1];
+      if (half == 0 && p.f.lse != nullptr) {              // every part of a row holds the same maximum
+        xch_m[ipar][0][row] = m_run[0];
+        xch_m[ipar][1][row] = m_run[1];
+      }
       if (p.use_tma) {
         // the epilogue warps take it from here; go straight on to the next item
         __syncwarp();
@@ -686,6 +694,8 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
         const int h = item_h[sx];
         const int tk = token[sx];
+        if (half == 0 && p.f.lse != nullptr && tk >= 0)
+          p.f.lse[(int64_t(item_b) * p.f.H + h) * p.f.prob.S + tk] = row_lse(m_run[sx], l_tot, p.f.scale_log2);
         __nv_bfloat16* dst = p.f.o + item_b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh + half * COLS;
         store_o_row(lane_addr + 256 + sx * 128 + half * COLS, COLS, inv, dst, tk >= 0, p.wide_stores != 0);
         ptx::tc_fence_before();
@@ -729,6 +739,8 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
           const int h = item_h[sx];
           const int tk = token[sx];
+          if (p.f.lse != nullptr && tk >= 0)
+            p.f.lse[(int64_t(item_b) * p.f.H + h) * p.f.prob.S + tk] = row_lse(xch_m[ipar][sx][row], l_tot, p.f.scale_log2);
           __nv_bfloat16* dst = p.f.o + item_b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + h * p.f.os.sh;
           store_o_row(lane_addr + 256 + sx * 128, 128, inv, dst, tk >= 0, p.wide_stores != 0);
           ptx::tc_fence_before();

@@ -241,7 +241,7 @@ size_t fwd_scratch_bytes(const Problem&) { return sizeof(int); }
 
 int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, int S, int H, int Hkv,
                const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, int family, int pattern,
-               int param, float softmax_scale, int device, void* stream) {
+               int param, float softmax_scale, int device, void* stream, float* lse = nullptr) {
   if (!q || !k || !v || !out || B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0) return INTRA_ERR_BAD_ARG;
   if (!qs || !ks || !vs || !os) return INTRA_ERR_BAD_ARG;
   if (!(softmax_scale > 0.f) || !std::isfinite(softmax_scale)) return INTRA_ERR_BAD_ARG;
@@ -270,6 +270,7 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
   p.B = B; p.H = H; p.Hkv = Hkv;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = g_dev[device].status_word;
+  p.lse = lse;
   // Everything runs on the persistent two-sub-tile kernel (Gather-0, whose tiles share no keys, with one
   // K / V buffer per sub-tile); INTRA_B200_SINGLE_TILE=1 forces the one-tile kernel, for A/B runs.
   static const bool force_single = [] { const char* v = std::getenv("INTRA_B200_SINGLE_TILE"); return v && v[0] == '1'; }();
@@ -330,6 +331,25 @@ int intra_b200_fwd_image(const void* q, const void* k, const void* v, void* out,
                          void* cuda_stream) {
   return launch_fwd(q, k, v, out, B, S, H, H, q_strides, k_strides, v_strides, out_strides, 1, pattern, width,
                     softmax_scale, device, cuda_stream);
+}
+
+int intra_b200_fwd_llm_lse(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int H,
+                           int Hkv, const int64_t q_strides[3], const int64_t k_strides[3],
+                           const int64_t v_strides[3], const int64_t out_strides[3], int pattern, int group_num,
+                           int window, float softmax_scale, int device, void* cuda_stream) {
+  if (!lse || reinterpret_cast<uintptr_t>(lse) % 4 != 0) return INTRA_ERR_BAD_ARG;
+  const int param = pattern == INTRA_LLM_WINDOW ? window : group_num;
+  return launch_fwd(q, k, v, out, B, S, H, Hkv, q_strides, k_strides, v_strides, out_strides, 0, pattern, param,
+                    softmax_scale, device, cuda_stream, lse);
+}
+
+int intra_b200_fwd_image_lse(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int H,
+                             const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                             const int64_t out_strides[3], int pattern, int width, float softmax_scale, int device,
+                             void* cuda_stream) {
+  if (!lse || reinterpret_cast<uintptr_t>(lse) % 4 != 0) return INTRA_ERR_BAD_ARG;
+  return launch_fwd(q, k, v, out, B, S, H, H, q_strides, k_strides, v_strides, out_strides, 1, pattern, width,
+                    softmax_scale, device, cuda_stream, lse);
 }
 
 const char* intra_b200_strerror(int status) {
@@ -507,6 +527,7 @@ int intra_b200_fwd_llm_noalloc(const void* q, const void* k, const void* v, void
   p.B = B; p.H = H; p.Hkv = Hkv;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = st.scratch;
+  p.lse = nullptr;
   intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, stream>>>(p);
   e = cudaGetLastError();
   return e == cudaSuccess ? INTRA_OK : cuda_fail(e);

@@ -62,7 +62,8 @@ def _empty_like(q):
     return out
 
 
-def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_scale=None, *, strict=True):
+def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_scale=None, *, strict=True,
+                   return_lse=False):
     """Causal prefill attention for language models.
 
     pattern="scatter": token i attends to earlier tokens j with j % group_num == i % group_num.
@@ -72,6 +73,9 @@ def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_
     Any seqlen works for scatter and window; gather1 keeps the reference's contract of
     group_num=8 and seqlen % 64 == 0 (intra_attn/interface.py:41-42). `strict=False` (not in the
     reference) lifts that restriction: the kernels handle Gather-1 for any group_num and seqlen.
+    `return_lse=True` (not in the reference, whose kernels compute the value and drop it) returns
+    `(out, lse)` with lse of shape (batch, heads, seqlen), float32: the log of each query's softmax
+    denominator, which is what merging attention over disjoint key sets needs.
     """
     q, k, v = _check(q, k, v)
     if strict and pattern == "gather1" and (group_num != 8 or q.shape[1] % (group_num * group_num)):
@@ -79,16 +83,21 @@ def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_
     pid = LLM_PATTERNS[pattern]
     out = _empty_like(q)
     B, S, H, _ = q.shape
-    rc = lib.intra_b200_fwd_llm(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H, k.shape[2],
-                                strides3(q), strides3(k), strides3(v), strides3(out), pid, int(group_num),
-                                int(window), _scale(q, softmax_scale), q.device.index,
-                                torch.cuda.current_stream(q.device).cuda_stream)
+    tail = (strides3(q), strides3(k), strides3(v), strides3(out), pid, int(group_num), int(window),
+            _scale(q, softmax_scale), q.device.index, torch.cuda.current_stream(q.device).cuda_stream)
+    if return_lse:
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+        rc = lib.intra_b200_fwd_llm_lse(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                        B, S, H, k.shape[2], *tail)
+    else:
+        rc = lib.intra_b200_fwd_llm(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H, k.shape[2],
+                                    *tail)
     if rc != 0:
         _raise(rc)
-    return out
+    return (out, lse) if return_lse else out
 
 
-def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *, strict=True):
+def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *, strict=True, return_lse=False):
     """Bidirectional attention for FLUX-style sequences: 512 text tokens followed by a
     width x width grid of image tokens.
 
@@ -97,7 +106,8 @@ def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *
     pattern="gather0": each 8 x 8 image patch attends to a 16 x 16 window around it plus all text.
 
     width must be 64 or 128 as in the reference (intra_attn/interface.py:60-63); `strict=False` (not in
-    the reference) accepts any width that is a multiple of 8 and at least 16.
+    the reference) accepts any width that is a multiple of 8 and at least 16. `return_lse=True` returns
+    `(out, lse)` as in intra_llm_attn.
     """
     q, k, v = _check(q, k, v)
     if not strict and (width < 16 or width % 8):
@@ -111,13 +121,17 @@ def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *
     pid = IMAGE_PATTERNS[pattern]
     out = _empty_like(q)
     B, S, H, _ = q.shape
-    rc = lib.intra_b200_fwd_image(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H,
-                                  strides3(q), strides3(k), strides3(v), strides3(out), pid, int(width),
-                                  _scale(q, softmax_scale), q.device.index,
-                                  torch.cuda.current_stream(q.device).cuda_stream)
+    tail = (strides3(q), strides3(k), strides3(v), strides3(out), pid, int(width), _scale(q, softmax_scale),
+            q.device.index, torch.cuda.current_stream(q.device).cuda_stream)
+    if return_lse:
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+        rc = lib.intra_b200_fwd_image_lse(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                          B, S, H, *tail)
+    else:
+        rc = lib.intra_b200_fwd_image(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H, *tail)
     if rc != 0:
         _raise(rc)
-    return out
+    return (out, lse) if return_lse else out
 
 
 def device_status(device=None, reset=False):

@@ -187,6 +187,27 @@ def masked_attention_rows(q, k, v, mask, softmax_scale=None, rows: int = 1024):
     return out
 
 
+def masked_lse(q, k, mask, softmax_scale=None, rows: int = 1024):
+    """log(sum_j exp(scale * q_i . k_j)) over the keys the mask lets query i attend, fp32, shape
+    (B, H, S): the `softmax_lse` the reference's bindings return (csrc/flash_attn/flash_api.cpp:470,
+    551) in the layout of its dense kernels."""
+    if not torch.is_tensor(mask):
+        mask = torch.from_numpy(np.ascontiguousarray(mask))
+    B, S, H, D = q.shape
+    Hkv = k.shape[2]
+    scale = 1.0 / math.sqrt(D) if softmax_scale is None else softmax_scale
+    kf = k.float().permute(0, 2, 3, 1)                       # B, Hkv, D, S
+    rep = H // Hkv
+    out = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    for r0 in range(0, S, rows):
+        r1 = min(r0 + rows, S)
+        qs = q[:, r0:r1].float().permute(0, 2, 1, 3).reshape(B, Hkv, rep, r1 - r0, D)
+        s = torch.matmul(qs, kf[:, :, None]) * scale         # B, Hkv, rep, rows, S
+        s = s.masked_fill(~mask[r0:r1].to(s.device), float("-inf"))
+        out[:, :, r0:r1] = torch.logsumexp(s, dim=-1).reshape(B, H, r1 - r0)
+    return out
+
+
 def make_inputs(B, S, H, Hkv, seed=0, device="cpu", D=128):
     """Seeded i.i.d. N(0, 1) bf16 q, k, v like the reference's test and benchmark inputs
     (tests/test_kernel.py:17-20, benchmarks/bench_kernel.py:45-49). Always drawn on the CPU so the

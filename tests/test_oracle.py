@@ -49,3 +49,21 @@ def test_attention_matches_reference_output(meta):
     assert torch.allclose(got.float(), want.float(), atol=2e-3, rtol=8e-3)
     rows = oracle.masked_attention_rows(q, k, v, mask, rows=200)
     assert torch.allclose(rows.float(), want.float(), atol=2e-3, rtol=8e-3)
+
+
+def test_masked_lse_matches_direct_logsumexp_and_softmax():
+    """The log-sum-exp oracle: equal to a direct logsumexp over the masked scores, slab size
+    irrelevant, and consistent with masked_attention (exp(s - lse) are its probabilities)."""
+    q, k, v = oracle.make_inputs(1, 300, 4, 2, seed=1)
+    mask = torch.from_numpy(oracle.llm_scatter_mask(300, 3))
+    lse = oracle.masked_lse(q, k, mask, rows=128)
+    assert lse.shape == (1, 4, 300) and lse.dtype == torch.float32
+    kf = k.float().repeat_interleave(2, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), kf) * 128 ** -0.5
+    s = s.masked_fill(~mask, float("-inf"))
+    assert float((torch.logsumexp(s, -1) - lse).abs().max()) <= 1e-5
+    assert torch.equal(lse, oracle.masked_lse(q, k, mask, rows=77))
+    p = torch.exp(s - lse[..., None])
+    out = torch.einsum("bhqk,bkhd->bqhd", p, v.float().repeat_interleave(2, dim=2))
+    ref = oracle.masked_attention(q, k, v, mask).float()
+    assert float((out - ref).abs().max()) <= 1e-2

@@ -274,3 +274,45 @@ def test_llm_backend_callable(lib):
     kk, vv = k.repeat_interleave(4, 1).float(), v.repeat_interleave(4, 1).float()
     att = torch.softmax(q[:, :, -1:].float() @ kk.transpose(-1, -2) * 128 ** -0.5, -1) @ vv
     assert _util.max_abs_err(out, att.transpose(1, 2)) <= _util.ATOL
+
+
+LSE_ATOL = 2e-3   # fp32 scores and sums; exponentials are ex2.approx / a cubic, both far below this
+
+
+@pytest.mark.parametrize("family,pattern,S,H,Hkv,param", [
+    ("llm", "scatter", 3000, 4, 2, 3),      # ragged groups, head pairs
+    ("llm", "gather1", 2048, 3, 3, 8),      # odd head count: row pairs
+    ("llm", "window", 2500, 4, 1, 576),
+    ("image", "scatter", 512 + 32 * 32, 2, 2, 32),
+    ("image", "gather0", 512 + 32 * 32, 2, 2, 32),
+])
+def test_lse_output(lib, family, pattern, S, H, Hkv, param):
+    """The optional log-sum-exp output against the oracle on every pattern; asking for it does not
+    change the attention output."""
+    from intra_b200 import intra_image_attn, intra_llm_attn
+    q, k, v = oracle.make_inputs(2, S, H, Hkv, seed=23, device="cuda")
+    kw = {"width": param} if family == "image" else ({"window": param} if pattern == "window" else {"group_num": param})
+    mask = oracle.build_mask(family, pattern, S, **kw)
+    ref = oracle.masked_lse(q, k, torch.from_numpy(mask).cuda())
+    fn = intra_image_attn if family == "image" else intra_llm_attn
+    with torch.no_grad():
+        plain = fn(q, k, v, pattern, strict=False, **kw)
+        out, lse = fn(q, k, v, pattern, strict=False, return_lse=True, **kw)
+    assert lse.shape == (2, H, S) and lse.dtype == torch.float32
+    assert torch.equal(out, plain)
+    assert bool(torch.isfinite(lse).all())
+    assert float((lse - ref).abs().max()) <= LSE_ATOL
+
+
+def test_lse_merges_disjoint_key_sets(lib):
+    """Two nested windows: the log-sum-exp grows with the key set, and by the log of the added mass,
+    which is the property a caller merging partial results relies on."""
+    from intra_b200 import intra_llm_attn
+    q, k, v = oracle.make_inputs(1, 2048, 2, 2, seed=29, device="cuda")
+    with torch.no_grad():
+        _, lse_small = intra_llm_attn(q, k, v, "window", window=256, return_lse=True)
+        _, lse_big = intra_llm_attn(q, k, v, "window", window=1024, return_lse=True)
+    assert bool((lse_big >= lse_small - 1e-4).all())
+    ref_small = oracle.masked_lse(q, k, torch.from_numpy(oracle.llm_window_mask(2048, 256)).cuda())
+    ref_big = oracle.masked_lse(q, k, torch.from_numpy(oracle.llm_window_mask(2048, 1024)).cuda())
+    assert float(((lse_big - lse_small) - (ref_big - ref_small)).abs().max()) <= 2 * LSE_ATOL
