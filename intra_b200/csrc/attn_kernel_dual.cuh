@@ -595,13 +595,29 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 1);
 
           const int u0 = n * TILE_N + half * COLS;
-          if (lo[sx] > u0 || hi[sx] < u0 + COLS - 1) {    // this row's interval does not cover these columns
+          // Rows whose key interval does not cover these columns (diagonal and window-edge tiles) mask
+          // the scores outside it. Short items (the 4-way instantiation) meet such tiles often: there the
+          // test is one unsigned compare and a select per score - with || on two signed compares it
+          // compiles to a divergent branch per score, 1300 clocks a phase - behind a warp-wide vote, which
+          // keeps the selects out of the other tiles' instruction stream. Long items keep the plain form,
+          // which the compiler schedules better around their rarely taken branch.
+          if constexpr (NSPLIT == 4) {
+            if (__any_sync(0xffffffffu, lo[sx] > u0 || hi[sx] < u0 + COLS - 1)) {
+              const int first = lo[sx] - u0;
+              const unsigned span = unsigned(hi[sx] - lo[sx]);
 #pragma unroll
-            for (int c = 0; c < COLS; ++c) {
-              const int u = u0 + c;
-              if (u < lo[sx] || u > hi[sx]) s[c] = -CUDART_INF_F;
+              for (int c = 0; c < COLS; ++c) s[c] = unsigned(c - first) > span ? -CUDART_INF_F : s[c];
+            }
+          } else {
+            if (lo[sx] > u0 || hi[sx] < u0 + COLS - 1) {
+#pragma unroll
+              for (int c = 0; c < COLS; ++c) {
+                const int u = u0 + c;
+                if (u < lo[sx] || u > hi[sx]) s[c] = -CUDART_INF_F;
+              }
             }
           }
+          if (NSPLIT == 4) INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 7);
           const float my_max = sm::row_max(s);
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 5);
           xch_max[ph & 1][half][row] = my_max;
