@@ -617,7 +617,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
               }
             }
           }
-          if (NSPLIT == 4) INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 7);
           const float my_max = sm::row_max(s);
           INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 5);
           xch_max[ph & 1][half][row] = my_max;
