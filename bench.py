@@ -39,9 +39,9 @@ if ROOT not in sys.path:
 
 HEAD_DIM = 128
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
-# dram__bytes_read.sum + dram__bytes_write.sum of one Gather-1 launch of the default workload, from
-# the ncu capture summarised under profiles/.
-NCU_TRAFFIC_BYTES = {"c2": 290626048 + 98915840}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of each workload's dominant kernel (c2:
+# Gather-1, c3: image Scatter, c4: Scatter G=2), from the ncu captures summarised under profiles/.
+NCU_TRAFFIC_BYTES = {"c2": 289179392 + 99074560, "c3": 385995264 + 90712832, "c4": 1797749000 + 241139968}
 
 WORKLOADS = {
     # name: (description, B, S, H, Hkv, [(family, pattern, kwargs)])
@@ -96,6 +96,9 @@ def load_peaks():
             d = json.load(f)
         return d, "measured"
     return dict(FALLBACK_PEAKS), "fallback"
+
+
+CLOCK_TAIL_S = 0.25   # how long the timed launches are kept running past the end event for the clock sampler
 
 
 class ClockSampler:
@@ -165,7 +168,8 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         reasons = sorted({r for s in self.samples for r in s[2]})
         return {"sm_mhz": statistics.median(s[0] for s in self.samples),
-                "sm_max_mhz": max(s[1] for s in self.samples), "reasons": reasons, "samples": len(self.samples)}
+                "sm_max_mhz": max(s[1] for s in self.samples), "reasons": reasons, "samples": len(self.samples),
+                "window": "the timed steps plus %.2f s of the same launches right after them" % CLOCK_TAIL_S}
 
 
 class CpuSample:
@@ -306,6 +310,15 @@ def run_ours(args):
                     run_call(c, q, k, v)
                     evs[s][i][1].record(stream)
             t_end.record(stream)
+            # The timed region of the default workload lasts tens of milliseconds, less than one NVML
+            # query under load takes, so the same launches keep running (after the end event: untimed,
+            # uncounted) until the sampler has watched this load for a quarter of a second.
+            t_tail = time.perf_counter()
+            while time.perf_counter() - t_tail < CLOCK_TAIL_S:
+                for _ in range(10):
+                    for c in calls:
+                        run_call(c, q, k, v)
+                torch.cuda.synchronize()
             barrier()
         total_ms = t_beg.elapsed_time(t_end)
         launch_ms = [statistics.mean(evs[s][i][0].elapsed_time(evs[s][i][1]) for s in range(args.steps))
