@@ -1,17 +1,21 @@
 // Persistent, ping-pong forward kernel: each CTA owns one SM and walks a static list of pair tiles
 // (intra_index.h): two 128-row query sub-tiles that share every K / V tile brought into shared
-// memory. While one sub-tile's softmax runs on the CUDA cores, the tensor core works on the
-// other's QK^T and PV, so the two pipes overlap inside one CTA:
+// memory (or, for Gather-0, keep a K / V buffer each). While one sub-tile's softmax runs on the CUDA
+// cores, the tensor core works on the other's QK^T and PV, so the two pipes overlap inside one CTA.
 //
-//   softmax warps (8 or 16)  softmax / correction, alternating between the sub-tiles: warpgroup j owns score
-//                columns [j * 128 / NSPLIT, (j + 1) * 128 / NSPLIT) of every row of BOTH sub-tiles
-//                (TMEM: S0 cols 0-127, S1 cols 128-255, O0 cols 256-383, O1 cols 384-511)
-//   next 4 warps when the tiles are TMA boxes: epilogue warps (O of a finished item -> bf16 -> global while
-//                the softmax warps are already on the next item); otherwise loaders: index maps +
-//                cp.async row gathers, completion signalled by the copies themselves
-//   then: a warp whose elected thread issues tcgen05.mma (below) and a warp with one thread that issues the TMA loads of Q0, Q1 and a 2-stage ring each for K, V
-//   warp 12      one thread issues tcgen05.mma in the order QK0(n) PV1(n-1) QK1(n) PV0(n), carried on
-//                across tile boundaries so the next tile's first QK^T overlaps this tile's last softmax
+// Warp roles (N = softmax column split, 2 or 4):
+//   warps [0, 4N)      softmax / correction, all on one sub-tile at a time, alternating between the two:
+//                      warp w owns rows 32 (w % 4) .. +31 and score columns [(w / 4) * 128 / N, +128 / N)
+//                      (TMEM: S0 cols 0-127, S1 cols 128-255, O0 cols 256-383, O1 cols 384-511; P overlays S)
+//   warps [4N, 4N+4)   with TMA loads: epilogue (O of a finished item -> bf16 -> global while the softmax
+//                      warps are already on the next item); otherwise loaders: index maps + cp.async row
+//                      gathers whose completion the copies signal themselves
+//   warp 4N+4          an elected thread issues tcgen05.mma in the order QK0(n) PV1(n-1) QK1(n) PV0(n),
+//                      carried across item boundaries so that the next item's first QK^T overlaps this
+//                      item's last softmax
+//   warp 4N+5          one thread issues the TMA loads: Q0, Q1 and a 2-stage ring each for K and V
+//   warp 4N+6          planner: decodes the CTA's items a few ahead into a ring in shared memory (key-tile
+//                      count, per-row token and key interval, TMA box coordinates) for all other roles
 //
 // Items are dealt to CTAs heaviest first in boustrophedon order, which needs no counters in global
 // memory. Every wait is bounded; see attn_kernel.cuh for the abort protocol, which is the same.
@@ -19,11 +23,11 @@
 // A tcgen05.commit costs the tensor pipe about as much as one MMA, so only two are issued per key tile:
 // after QK0 (S0 ready) and after QK1 (S1 ready). Because the pipe completes in issue order the second
 // one also tells the loaders that the K stage of that tile, the V stage of the tile before it and - on
-// a tile's last key tile - the Q buffers may be overwritten; it alternates between two barriers so
+// an item's last key tile - the Q buffers may be overwritten; it alternates between two barriers so
 // that waiters a tile ahead or behind can never confuse phases. O is signalled once per item.
 //
 // Replaces, like attn_kernel.cuh, the reference's compute_attn_1rowblock_* kernels
-// (csrc/flash_attn/src/flash_fwd_kernel.h:3970-6158) for every pattern whose tiles pair up.
+// (csrc/flash_attn/src/flash_fwd_kernel.h:3970-6158) for every pattern.
 #pragma once
 #include "attn_kernel.cuh"
 #include "softmax.cuh"
