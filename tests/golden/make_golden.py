@@ -76,7 +76,9 @@ def bits(x):
 
 
 def main():
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of the reference repository>")
+    ref = load_reference(sys.argv[1])
     torch.set_num_threads(os.cpu_count())
 
     masks = []
