@@ -316,3 +316,43 @@ def test_lse_merges_disjoint_key_sets(lib):
     ref_small = oracle.masked_lse(q, k, torch.from_numpy(oracle.llm_window_mask(2048, 256)).cuda())
     ref_big = oracle.masked_lse(q, k, torch.from_numpy(oracle.llm_window_mask(2048, 1024)).cuda())
     assert float(((lse_big - lse_small) - (ref_big - ref_small)).abs().max()) <= 2 * LSE_ATOL
+
+
+_FORCED_MODE_SCRIPT = r"""
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+from oracle import intra_oracle as oracle
+from intra_b200 import intra_llm_attn, intra_image_attn
+worst = 0.0
+with torch.no_grad():
+    for family, pattern, S, H, Hkv, kw in (
+            ("llm", "scatter", 2048, 4, 2, {"group_num": 2}), ("llm", "gather1", 2048, 3, 3, {"group_num": 8}),
+            ("llm", "window", 1536, 4, 1, {"window": 576}), ("image", "scatter", 512 + 32 * 32, 2, 2, {"width": 32}),
+            ("image", "gather0", 512 + 32 * 32, 2, 2, {"width": 32})):
+        q, k, v = oracle.make_inputs(1, S, H, Hkv, seed=31, device="cuda")
+        fn = intra_image_attn if family == "image" else intra_llm_attn
+        out, lse = fn(q, k, v, pattern, strict=False, return_lse=True, **kw)
+        mask = torch.from_numpy(oracle.build_mask(family, pattern, S, **kw)).cuda()
+        ref = oracle.masked_attention(q, k, v, mask)
+        worst = max(worst, float((out.float() - ref.float()).abs().max()))
+        assert float((lse - oracle.masked_lse(q, k, mask)).abs().max()) <= 2e-3, (family, pattern)
+print("WORST", worst)
+assert worst <= 1.6e-2
+"""
+
+
+@pytest.mark.parametrize("env", [{"INTRA_B200_SOFTMAX_SPLIT": "2"}, {"INTRA_B200_SOFTMAX_SPLIT": "4"},
+                                 {"INTRA_B200_NO_TMA": "1"}, {"INTRA_B200_NO_TMA": "1", "INTRA_B200_SOFTMAX_SPLIT": "2"},
+                                 {"INTRA_B200_SINGLE_TILE": "1"}], ids=lambda e: ",".join(f"{k[11:]}={v}" for k, v in e.items()))
+def test_forced_kernel_paths(lib, env):
+    """Every kernel path the launcher can choose, forced through its environment switches (read once
+    per process, hence a child process): both softmax splits for every pattern, including the
+    combinations the heuristic never picks, the cp.async loaders, and the first-generation kernel."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run([sys.executable, "-c", _FORCED_MODE_SCRIPT, root], env={**os.environ, **env},
+                          capture_output=True, text=True, timeout=600, cwd=root)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert "WORST" in proc.stdout
