@@ -63,3 +63,38 @@ def test_row_pair_visited_set_equals_mask(lib, case):
     assert counts.max() <= 1
     mask = oracle.build_mask(case["family"], case["pattern"], S, **_util.case_kwargs(case))
     assert np.array_equal(counts.view(bool), mask)
+
+
+def _check_random_shape(lib, family, pattern, S, param):
+    kw = ({"width": param} if family == "image" else
+          {"window": param} if pattern == "window" else {"group_num": param})
+    mask = oracle.build_mask(family, pattern, S, **kw)
+    for fn in (lib.intra_b200_visited_host, lib.intra_b200_visited_pairs_host):
+        counts = np.zeros((S, S), dtype=np.uint8)
+        rc = fn(_util.FAMILY[family], _util.PATTERN_ID[(family, pattern)], S, param, counts.ctypes.data)
+        assert rc == 0, (family, pattern, S, param, rc)
+        assert counts.max() <= 1
+        assert np.array_equal(counts.view(bool), mask), (family, pattern, S, param)
+
+
+def test_random_llm_shapes_visit_exactly_the_mask(lib):
+    """Seeded sweep over shapes the fixed matrix does not hold: ragged group lengths, sequences
+    shorter than a tile, group counts that do not divide anything, windows that are not block
+    multiples - both the tile and the pair-tile decomposition."""
+    rng = np.random.default_rng(20240611)
+    for _ in range(60):
+        S = int(rng.integers(1, 900))
+        G = int(rng.integers(1, min(S, 13) + 1))
+        _check_random_shape(lib, "llm", "scatter", S, G)
+        _check_random_shape(lib, "llm", "gather1", S, G)
+        W = int(rng.integers(64, 1100))
+        _check_random_shape(lib, "llm", "window", S, W)
+
+
+@pytest.mark.parametrize("width", [16, 24, 40, 56])
+def test_odd_image_widths_visit_exactly_the_mask(lib, width):
+    """Widths beyond the reference's 64 and 128: an odd number of patches per row leaves a patch
+    without a partner, and width / 4 need not divide a tile."""
+    S = 512 + width * width
+    _check_random_shape(lib, "image", "scatter", S, width)
+    _check_random_shape(lib, "image", "gather0", S, width)
