@@ -275,11 +275,11 @@ def run_ours(args):
     q, k, v = hq.to(dev), hk.to(dev), hv.to(dev)
     houts = [torch.empty_like(hq).pin_memory() for _ in calls]
 
-    def run_call(c, q_, k_, v_):
+    def run_call(c, q_, k_, v_, out=None):
         family, pattern, kw = c
         if family == "llm":
-            return intra_llm_attn(q_, k_, v_, pattern, **kw)
-        return intra_image_attn(q_, k_, v_, pattern, **kw)
+            return intra_llm_attn(q_, k_, v_, pattern, out=out, **kw)
+        return intra_image_attn(q_, k_, v_, pattern, out=out, **kw)
 
     flops_calls = [call_flops(f, p, kw, S, H) for f, p, kw in calls]
     flops_step = sum(flops_calls)
@@ -331,6 +331,9 @@ def run_ours(args):
         e_steps = max(3, min(args.steps, 20))
         s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
         dbuf = [(torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)) for _ in range(2)]
+        # outputs are double-buffered device tensors of the caller's too (out=): an allocation per call
+        # on a side stream makes the caching allocator go back to cudaMalloc while copies are in flight
+        obuf = [[torch.empty_like(q) for _ in calls] for _ in range(2)]
         ev_in = [torch.cuda.Event() for _ in range(2)]      # inputs of the slot have landed
         ev_cmp = [torch.cuda.Event() for _ in range(2)]     # kernels of the slot are done (inputs reusable)
         ev_out = [torch.cuda.Event() for _ in range(2)]     # outputs of the slot are on the host
@@ -347,13 +350,14 @@ def run_ours(args):
                     ev_in[slot].record(s_in)
                 with torch.cuda.stream(s_cmp):
                     s_cmp.wait_event(ev_in[slot])
-                    outs = [run_call(c, *dbuf[slot]) for c in calls]
+                    if st >= 2:
+                        s_cmp.wait_event(ev_out[slot])           # the slot's previous outputs are on the host
+                    outs = [run_call(c, *dbuf[slot], out=obuf[slot][i]) for i, c in enumerate(calls)]
                     ev_cmp[slot].record(s_cmp)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_cmp[slot])
                     for i, o in enumerate(outs):
                         houts[i].copy_(o, non_blocking=True)
-                        o.record_stream(s_out)
                     ev_out[slot].record(s_out)
 
         for st_ in (s_in, s_cmp, s_out):

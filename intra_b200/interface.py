@@ -55,7 +55,14 @@ def _raise(status):
     raise ValueError(f"intra_b200: {msg}")
 
 
-def _empty_like(q):
+def _empty_like(q, out=None):
+    """The output tensor: the caller's `out` after checks, else a fresh tensor laid out like q."""
+    if out is not None:
+        if out.shape != q.shape or out.dtype != q.dtype or out.device != q.device:
+            raise ValueError("out must match q in shape, dtype and device")
+        if out.stride(-1) != 1 or any(out.stride(d) % 8 for d in range(3)) or out.data_ptr() % 16:
+            raise ValueError("out needs unit stride in the last dim and 16-byte aligned rows")
+        return out
     out = torch.empty_like(q)
     if out.stride(-1) != 1 or any(out.stride(d) % 8 for d in range(3)):
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
@@ -63,7 +70,7 @@ def _empty_like(q):
 
 
 def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_scale=None, *, strict=True,
-                   return_lse=False):
+                   return_lse=False, out=None):
     """Causal prefill attention for language models.
 
     pattern="scatter": token i attends to earlier tokens j with j % group_num == i % group_num.
@@ -75,13 +82,14 @@ def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_
     reference) lifts that restriction: the kernels handle Gather-1 for any group_num and seqlen.
     `return_lse=True` (not in the reference, whose kernels compute the value and drop it) returns
     `(out, lse)` with lse of shape (batch, heads, seqlen), float32: the log of each query's softmax
-    denominator, which is what merging attention over disjoint key sets needs.
+    denominator, which is what merging attention over disjoint key sets needs. `out=` (not in the
+    reference, which always allocates) writes into a tensor of the caller's; it must not alias q, k, v.
     """
     q, k, v = _check(q, k, v)
     if strict and pattern == "gather1" and (group_num != 8 or q.shape[1] % (group_num * group_num)):
         raise ValueError(f"gather1 needs group_num=8 and seqlen % 64 == 0, got G={group_num}, S={q.shape[1]}")
     pid = LLM_PATTERNS[pattern]
-    out = _empty_like(q)
+    out = _empty_like(q, out)
     B, S, H, _ = q.shape
     tail = (strides3(q), strides3(k), strides3(v), strides3(out), pid, int(group_num), int(window),
             _scale(q, softmax_scale), q.device.index, torch.cuda.current_stream(q.device).cuda_stream)
@@ -97,7 +105,8 @@ def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_
     return (out, lse) if return_lse else out
 
 
-def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *, strict=True, return_lse=False):
+def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *, strict=True, return_lse=False,
+                     out=None):
     """Bidirectional attention for FLUX-style sequences: 512 text tokens followed by a
     width x width grid of image tokens.
 
@@ -107,7 +116,7 @@ def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *
 
     width must be 64 or 128 as in the reference (intra_attn/interface.py:60-63); `strict=False` (not in
     the reference) accepts any width that is a multiple of 8 and at least 16. `return_lse=True` returns
-    `(out, lse)` as in intra_llm_attn.
+    `(out, lse)` and `out=` writes into the caller's tensor, as in intra_llm_attn.
     """
     q, k, v = _check(q, k, v)
     if not strict and (width < 16 or width % 8):
@@ -119,7 +128,7 @@ def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *
     if k.shape[2] != q.shape[2]:
         raise ValueError("image attention is multi-head: k/v need as many heads as q")
     pid = IMAGE_PATTERNS[pattern]
-    out = _empty_like(q)
+    out = _empty_like(q, out)
     B, S, H, _ = q.shape
     tail = (strides3(q), strides3(k), strides3(v), strides3(out), pid, int(width), _scale(q, softmax_scale),
             q.device.index, torch.cuda.current_stream(q.device).cuda_stream)

@@ -356,3 +356,27 @@ def test_forced_kernel_paths(lib, env):
                           capture_output=True, text=True, timeout=600, cwd=root)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
     assert "WORST" in proc.stdout
+
+
+def test_out_argument(lib):
+    """out= writes into the caller's tensor (any layout the kernels accept) and refuses one that
+    does not match."""
+    from intra_b200 import intra_image_attn, intra_llm_attn
+    q, k, v = oracle.make_inputs(1, 1024, 4, 2, seed=37, device="cuda")
+    with torch.no_grad():
+        want = intra_llm_attn(q, k, v, "scatter", group_num=4)
+        out = torch.full_like(q, float("nan"))
+        got = intra_llm_attn(q, k, v, "scatter", group_num=4, out=out)
+        assert got is out and torch.equal(out, want)
+        view = torch.zeros(1, 4, 1024, 128, dtype=torch.bfloat16, device="cuda").transpose(1, 2)   # (B, H, S, D) storage
+        intra_llm_attn(q, k, v, "scatter", group_num=4, out=view)
+        assert torch.equal(view, want)
+        with pytest.raises(ValueError):
+            intra_llm_attn(q, k, v, "scatter", group_num=4, out=torch.empty(1, 1024, 4, 64, dtype=torch.bfloat16, device="cuda"))
+        with pytest.raises(ValueError):
+            intra_llm_attn(q, k, v, "scatter", group_num=4, out=torch.empty_like(q, dtype=torch.float16))
+        qi, ki, vi = oracle.make_inputs(1, 512 + 16 * 16, 2, 2, seed=38, device="cuda")
+        wi = intra_image_attn(qi, ki, vi, "gather0", 16, strict=False)
+        oi = torch.empty_like(qi)
+        intra_image_attn(qi, ki, vi, "gather0", 16, strict=False, out=oi)
+        assert torch.equal(oi, wi)
