@@ -55,9 +55,11 @@ def _raise(status):
     raise ValueError(f"intra_b200: {msg}")
 
 
-def _empty_like(q, out=None):
+def _empty_like(q, out=None, inputs=()):
     """The output tensor: the caller's `out` after checks, else a fresh tensor laid out like q."""
     if out is not None:
+        if any(out.data_ptr() == x.data_ptr() for x in inputs):
+            raise ValueError("out must not alias q, k or v: other tiles still read them while it is written")
         if out.shape != q.shape or out.dtype != q.dtype or out.device != q.device:
             raise ValueError("out must match q in shape, dtype and device")
         if out.stride(-1) != 1 or any(out.stride(d) % 8 for d in range(3)) or out.data_ptr() % 16:
@@ -89,7 +91,7 @@ def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_
     if strict and pattern == "gather1" and (group_num != 8 or q.shape[1] % (group_num * group_num)):
         raise ValueError(f"gather1 needs group_num=8 and seqlen % 64 == 0, got G={group_num}, S={q.shape[1]}")
     pid = LLM_PATTERNS[pattern]
-    out = _empty_like(q, out)
+    out = _empty_like(q, out, (q, k, v))
     B, S, H, _ = q.shape
     tail = (strides3(q), strides3(k), strides3(v), strides3(out), pid, int(group_num), int(window),
             _scale(q, softmax_scale), q.device.index, torch.cuda.current_stream(q.device).cuda_stream)
@@ -128,7 +130,7 @@ def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *
     if k.shape[2] != q.shape[2]:
         raise ValueError("image attention is multi-head: k/v need as many heads as q")
     pid = IMAGE_PATTERNS[pattern]
-    out = _empty_like(q, out)
+    out = _empty_like(q, out, (q, k, v))
     B, S, H, _ = q.shape
     tail = (strides3(q), strides3(k), strides3(v), strides3(out), pid, int(width), _scale(q, softmax_scale),
             q.device.index, torch.cuda.current_stream(q.device).cuda_stream)

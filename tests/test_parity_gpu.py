@@ -375,6 +375,8 @@ def test_out_argument(lib):
             intra_llm_attn(q, k, v, "scatter", group_num=4, out=torch.empty(1, 1024, 4, 64, dtype=torch.bfloat16, device="cuda"))
         with pytest.raises(ValueError):
             intra_llm_attn(q, k, v, "scatter", group_num=4, out=torch.empty_like(q, dtype=torch.float16))
+        with pytest.raises(ValueError):
+            intra_llm_attn(q, k, v, "scatter", group_num=4, out=q)
         qi, ki, vi = oracle.make_inputs(1, 512 + 16 * 16, 2, 2, seed=38, device="cuda")
         wi = intra_image_attn(qi, ki, vi, "gather0", 16, strict=False)
         oi = torch.empty_like(qi)
