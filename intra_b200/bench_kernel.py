@@ -2,11 +2,18 @@
 
     python -m intra_b200.bench_kernel llm   [--seqlens 4096,...] [--groups 2,8] [--out file.json]
     python -m intra_b200.bench_kernel image [--out file.json]
+    python -m intra_b200.bench_kernel stack [--seqlens 32768] [--layers 32] [--out file.json]
 
 Same flags, same protocol (CUDA events around each call, 10 warm-ups, median of 50) and the same row
 keys as the reference's benchmarks/results/*.json, so B200 rows can sit next to its A100 ones; each
 sparse entry additionally gets `<key>_tflops`, the effective sparse TFLOP/s (4*128*H*attended pairs).
 The dense baseline is torch SDPA with K/V expanded to the query heads, as in the reference.
+
+`stack` runs the g2s4 layer schedule for real instead of extrapolating it from two timings as the
+reference's table does (benchmarks/bench_kernel.py:67): `--layers` attention calls back to back, layer l
+on its own seeded q/k/v (seed 1000 + l), Scatter G=2 on every eighth layer and window 576 on the others,
+timed as one region with CUDA events, against the same number of dense causal SDPA calls on the same
+tensors.
 """
 from __future__ import annotations
 
@@ -118,9 +125,52 @@ def bench_image(args):
     return rows
 
 
+def stack_pattern(layer):
+    """g2s4: Scatter G=2 on layers 0, 8, 16, 24, window 576 on the other 28."""
+    return ("scatter", {"group_num": 2}) if layer % 8 == 0 else ("window", {"window": 576})
+
+
+@torch.no_grad()
+def bench_stack(args):
+    rows = []
+    for S in args.seqlens:
+        layers = []
+        for layer in range(args.layers):
+            g = torch.Generator(device="cuda").manual_seed(1000 + layer)
+            mk = lambda h: torch.randn(args.batch, S, h, 128, device="cuda", dtype=torch.float32, generator=g).to(torch.bfloat16)
+            layers.append((mk(args.heads), mk(args.kv_heads), mk(args.kv_heads)))
+        out = torch.empty_like(layers[0][0])
+
+        def sparse_pass():
+            for layer, (q, k, v) in enumerate(layers):
+                pattern, kw = stack_pattern(layer)
+                intra_llm_attn(q, k, v, pattern, out=out, **kw)
+
+        def dense_pass():
+            for q, k, v in layers:
+                dense_sdpa(q, k, v, True)
+
+        r = {"seqlen": S, "layers": args.layers, "schedule": "g2s4",
+             "intra_ms": median_ms(sparse_pass, 2, args.stack_iters)}
+        flops = sum(4 * 128 * args.heads * args.batch *
+                    (llm_pairs("scatter", S, 2) if layer % 8 == 0 else llm_pairs("window", S, W=576))
+                    for layer in range(args.layers))
+        r["intra_tflops"] = flops / r["intra_ms"] / 1e9
+        try:
+            r["dense_ms"] = median_ms(dense_pass, 1, args.stack_iters)
+            r["speedup_vs_dense"] = r["dense_ms"] / r["intra_ms"]
+        except RuntimeError:
+            r["dense_ms"] = None
+        rows.append(r)
+        print("  ".join(f"{a}={b:.3f}" if isinstance(b, float) else f"{a}={b}" for a, b in r.items()), flush=True)
+    return rows
+
+
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("mode", choices=["llm", "image"])
+    p.add_argument("mode", choices=["llm", "image", "stack"])
+    p.add_argument("--layers", type=int, default=32)
+    p.add_argument("--stack-iters", type=int, default=5)
     p.add_argument("--seqlens", default="4096,8192,16384,32768,65536")
     p.add_argument("--groups", default="2,8")
     p.add_argument("--batch", type=int, default=1)
@@ -134,7 +184,9 @@ def main():
     args.seqlens = [int(x) for x in args.seqlens.split(",")]
     args.groups = [int(x) for x in args.groups.split(",")]
     print(f"device: {torch.cuda.get_device_name()}  torch {torch.__version__}")
-    rows = bench_llm(args) if args.mode == "llm" else bench_image(args)
+    if args.mode == "stack" and args.seqlens == [4096, 8192, 16384, 32768, 65536]:
+        args.seqlens = [32768]
+    rows = {"llm": bench_llm, "image": bench_image, "stack": bench_stack}[args.mode](args)
     if args.out:
         with open(args.out, "w") as f:
             json.dump({"device": torch.cuda.get_device_name(), "torch": torch.__version__,
