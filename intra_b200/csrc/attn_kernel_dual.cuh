@@ -83,7 +83,7 @@ struct DualParams {
   int heads_per_item;   // row_pairs ? H : H / 2  (number of items per pair tile and batch)
   int n_items;          // n_pair_tiles * B * heads_per_item
   int split_kv;         // the two sub-tiles keep their own key lists (Gather-0): K / V buffer s belongs to sub-tile s
-  int use_tma;          // tiles are fetched as TMA boxes (tma_maps.h) instead of cp.async row gathers
+  int use_tma;          // tiles are fetched as TMA boxes (tma_maps.h) instead of cp.async row gathers; selects kTma
   int wide_stores;      // every output row is 32-byte aligned: 256-bit global stores
   TmaMaps maps;
 };
@@ -443,7 +443,7 @@ __device__ __forceinline__ void split_loader(const DualParams& p, const SplitLoa
   if (!kTma) { ptx::cp_async_commit(); ptx::cp_async_wait<0>(); }
 }
 
-template <int NSPLIT, bool kSplitKV>
+template <int NSPLIT, bool kSplitKV, bool kTma>
 __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_kernel(const __grid_constant__ DualParams p) {
   using Cfg = DualCfg<NSPLIT>;
   constexpr int COLS = Cfg::COLS, SM_WARPS = Cfg::SM_WARPS, SM_THREADS = Cfg::SM_THREADS;
@@ -493,7 +493,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
 
   if (tid == 0) {
     abort_flag = 0;
-    const uint32_t producers = p.use_tma ? 1 : 128;       // one TMA-issuing thread, or every loader thread
+    const uint32_t producers = kTma ? 1 : 128;       // one TMA-issuing thread, or every loader thread
     ptx::mbar_init(q_full, producers);
     ptx::mbar_init(q1_full, producers);
     for (int j = 0; j < KV_STAGES; ++j) {
@@ -513,11 +513,11 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     ptx::mbar_init(drain, 1);
     ptx::mbar_init(xbar, SM_WARPS);                       // one arrival per softmax warp
     ptx::mbar_init(l_ready, SM_WARPS);
-    ptx::mbar_init(&o_free[0], p.use_tma ? 128 : SM_THREADS);   // whoever runs the epilogue
-    ptx::mbar_init(&o_free[1], p.use_tma ? 128 : SM_THREADS);
+    ptx::mbar_init(&o_free[0], kTma ? 128 : SM_THREADS);   // whoever runs the epilogue
+    ptx::mbar_init(&o_free[1], kTma ? 128 : SM_THREADS);
     // ring consumers, one arrival per warp: softmax warps, the MMA warp, and either the four epilogue warps
     // plus the TMA thread, or the four cp.async loader warps
-    const uint32_t consumers = SM_WARPS + 1 + (p.use_tma ? 5 : 4);
+    const uint32_t consumers = SM_WARPS + 1 + (kTma ? 5 : 4);
     for (int r = 0; r < ITEM_RING; ++r) {
       ptx::mbar_init(&slot_ready[r], 1);
       ptx::mbar_init(&slot_free[r], consumers);
@@ -688,7 +688,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
         xch_m[ipar][0][row] = m_run[0];
         xch_m[ipar][1][row] = m_run[1];
       }
-      if (p.use_tma) {
+      if (kTma) {
         // the epilogue warps take it from here; go straight on to the next item
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(l_ready);
@@ -732,7 +732,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     bool ok = true;
     int n_done = 0;
 
-    if (p.use_tma) {
+    if (kTma) {
       // ---- epilogue warps: O of a finished item -> global, while the softmax warps are already on
       //      the next item. Thread = query row (all 128 columns). ------------------------------------
       const int row = tid & 127;
@@ -843,11 +843,11 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
   } else {
     // ================================ MMA issue ==================================================
     ptx::setmaxnreg_dec<MMA_REGS>();
-    if (kSplitKV && warp == SM_WARPS + 5 && p.use_tma && lane == 0) {
+    if (kSplitKV && warp == SM_WARPS + 5 && kTma && lane == 0) {
       const SplitLoaderCtx cx = {q_smem0, k_smem0, v_smem0, q_full, q1_full, k_full, v_full, s0_full, s1_full,
                                  ring, slot_ready, slot_free, abort_p};
       split_loader<true>(p, cx, 0);
-    } else if (warp == SM_WARPS + 5 && p.use_tma && lane == 0) {
+    } else if (warp == SM_WARPS + 5 && kTma && lane == 0) {
       // ---- one thread drives the TMA unit ------------------------------------------------------------
       uint32_t kc = 0;                                    // K / V tiles requested so far (ring position)
       bool ok = true;
@@ -906,7 +906,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       }
     } else if (warp == SM_WARPS + 6) {
       // ---- planner: keeps the item ring filled -------------------------------------------------------
-      plan_items(p, ring, slot_ready, slot_free, cta, n_cta, lane, p.use_tma && !kSplitKV, abort_p);
+      plan_items(p, ring, slot_ready, slot_free, cta, n_cta, lane, kTma && !kSplitKV, abort_p);
     }
     if (warp == SM_WARPS + 4) {
       uint32_t kc = 0;                                    // key tiles issued so far

@@ -64,13 +64,21 @@ void init_device(int device) {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
   st.sm_count = prop.multiProcessorCount;
   if (e == cudaSuccess) e = cudaMalloc(&st.status_word, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(st.status_word, 0, sizeof(int));
@@ -300,10 +308,16 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
     static const int force_split = [] { const char* v = std::getenv("INTRA_B200_SOFTMAX_SPLIT"); return v ? std::atoi(v) : 0; }();
     const bool four = force_split ? force_split == 4 : (n_tiles > 0 && n_kv < 24 * n_tiles);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (four && d.split_kv) intra_fwd_dual_kernel<4, true><<<grid, DualCfg<4>::THREADS, DUAL_SMEM_BYTES, st>>>(d);
-    else if (four) intra_fwd_dual_kernel<4, false><<<grid, DualCfg<4>::THREADS, DUAL_SMEM_BYTES, st>>>(d);
-    else if (d.split_kv) intra_fwd_dual_kernel<2, true><<<grid, DualCfg<2>::THREADS, DUAL_SMEM_BYTES, st>>>(d);
-    else intra_fwd_dual_kernel<2, false><<<grid, DualCfg<2>::THREADS, DUAL_SMEM_BYTES, st>>>(d);
+#define INTRA_LAUNCH_DUAL(N, SPLIT) \
+    do { \
+      if (d.use_tma) intra_fwd_dual_kernel<N, SPLIT, true><<<grid, DualCfg<N>::THREADS, DUAL_SMEM_BYTES, st>>>(d); \
+      else intra_fwd_dual_kernel<N, SPLIT, false><<<grid, DualCfg<N>::THREADS, DUAL_SMEM_BYTES, st>>>(d); \
+    } while (0)
+    if (four && d.split_kv) INTRA_LAUNCH_DUAL(4, true);
+    else if (four) INTRA_LAUNCH_DUAL(4, false);
+    else if (d.split_kv) INTRA_LAUNCH_DUAL(2, true);
+    else INTRA_LAUNCH_DUAL(2, false);
+#undef INTRA_LAUNCH_DUAL
   } else {
     intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
   }
