@@ -322,6 +322,25 @@ def run_ours(args):
                 torch.cuda.synchronize()
             barrier()
         total_ms = t_beg.elapsed_time(t_end)
+
+        # ---- optional: the same steps with every call's head-sharded output all-gathered over NCCL
+        # into the full (B, S, H, 128) tensor on every rank, for callers that need it (reported beside
+        # the headline, never part of it)
+        gather_ms = 0.0
+        if args.gather_outputs and args.shard_heads and world > 1:
+            from intra_b200.sharded import gather_heads
+            for _ in range(3):
+                for i, c in enumerate(calls):
+                    gather_heads(run_call(c, q, k, v, out=res[i]))
+            g_beg, g_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            g_beg.record(stream)
+            for _ in range(args.steps):
+                for i, c in enumerate(calls):
+                    gather_heads(run_call(c, q, k, v, out=res[i]))
+            g_end.record(stream)
+            barrier()
+            gather_ms = g_beg.elapsed_time(g_end)
         launch_ms = [statistics.mean(evs[s][i][0].elapsed_time(evs[s][i][1]) for s in range(args.steps))
                      for i in range(len(calls))]
 
@@ -382,10 +401,10 @@ def run_ours(args):
     if status != 0:
         raise SystemExit(f"kernel status word {status}: a bounded wait gave up; numbers invalid")
 
-    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([total_ms, e2e_ms, gather_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = times.tolist()
+    total_ms, e2e_ms, gather_ms = times.tolist()
     if rank == 0:
         peaks, peaks_kind = load_peaks()
         ms_per_step = total_ms / args.steps
@@ -420,6 +439,12 @@ def run_ours(args):
                          "flops_per_launch": flops_calls[dom], "ms_per_launch": launch_ms[dom],
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
         }
+        if gather_ms > 0.0:
+            line["gather"] = {"ms_per_step": gather_ms / args.steps,
+                              "extra_ms_per_step": gather_ms / args.steps - ms_per_step,
+                              "bytes_received_per_rank_per_step": len(calls) * (world - 1) * q.numel() * 2,
+                              "what": "every call followed by an NCCL all-gather of its head-sharded output into the "
+                                      "full (B, S, H, 128) tensor on every rank (all_gather_into_tensor + head interleave)"}
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
             sample = CpuSample(args.workload, threads, stride=1)
@@ -443,6 +468,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--gather-outputs", action="store_true",
+                    help="with --shard-heads on several GPUs: also time the steps with every output all-gathered")
     ap.add_argument("--shard-heads", action="store_true",
                     help="strong scaling: split the workload's KV-head groups over the ranks instead of "
                          "giving every rank the whole workload")
