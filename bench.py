@@ -41,7 +41,7 @@ HEAD_DIM = 128
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of each workload's dominant kernel (c2:
 # Gather-1, c3: image Scatter, c4: Scatter G=2), from the ncu captures summarised under profiles/.
-NCU_TRAFFIC_BYTES = {"c2": 289179392 + 99074560, "c3": 385995264 + 90712832, "c4": 1797749000 + 241139968}
+NCU_TRAFFIC_BYTES = {"c2": 287272960 + 100174080, "c3": 385995264 + 90712832, "c4": 1797749000 + 241139968}
 
 WORKLOADS = {
     # name: (description, B, S, H, Hkv, [(family, pattern, kwargs)])
