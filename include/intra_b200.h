@@ -85,9 +85,23 @@ int intra_b200_last_cuda_error(void);
 
 /* Synchronises `device` and reads the word its kernels write when a bounded wait runs out
  * (0 = no kernel has given up since the last reset). `reset` != 0 clears it afterwards. Returns
- * INTRA_ERR_KERNEL when the word is non-zero. No counterpart in the reference, whose kernels have
- * no waits that can fail. */
+ * INTRA_ERR_KERNEL when the word is non-zero. The word keeps the FIRST failure (100 + the id of the
+ * wait site) until it is reset; kernels only ever write it, so a recorded failure does not change what
+ * later launches do: they run normally, and their outputs are valid if the word is still unchanged
+ * after them. The launch whose kernel gave up left some output rows unwritten. The entry points do
+ * not poll the word (that would need a host synchronisation per call); a caller that wants to know
+ * calls this function, e.g. once per step. It covers the regular entry points only:
+ * intra_b200_fwd_llm_noalloc reports through its own `prev_status` argument. No counterpart in the
+ * reference, whose kernels have no waits that can fail. */
 int intra_b200_device_status(int device, int* status_word, int reset);
+
+/* For the multi-GPU launcher (no counterpart in the reference, which runs on one GPU): reorders the
+ * result of an all-gather of head-sharded outputs, parts[world][rows][block_bytes] (rank-major), into
+ * out[rows][world][block_bytes], i.e. (batch, token, head, 128) order with rows = batch * tokens and
+ * block_bytes = heads per rank * 256. Device pointers, 16-byte aligned; block_bytes a multiple of 16;
+ * parts and out must not overlap. Asynchronous on `cuda_stream`. */
+int intra_b200_interleave_heads(const void* parts, void* out, int world, int64_t rows, int64_t block_bytes,
+                                int device, void* cuda_stream);
 
 /* Test hooks (the reference has no counterpart): the (query, key) pairs the index maps visit.
  * `family` 0 = llm, 1 = image; `param` = group_num (scatter, gather1), window, or width.
@@ -112,6 +126,40 @@ int intra_b200_tile_counts(int family, int pattern, int S, int param, int64_t* n
 int intra_b200_selftest_umma(const void* a, const void* b, const void* v, float p_scale,
                              float* s_out, float* o_out, int device, void* cuda_stream);
 
+/* Test hook: fetches every query tile and every key / value tile of a problem through the attention
+ * kernel's own TMA planning and load code (the counterpart of the reference's per-thread gather
+ * loaders, csrc/flash_attn/src/gmem_tile.h:270-1426) and reports which token row landed in which
+ * shared-memory row. q, k, v are device tensors as for the forward call whose rows encode their token
+ * id: elements 0..5 and 64..69 of token t's row hold (t + 1) % 256, (t + 1) / 256 % 256, (t + 1) / 65536,
+ * the head, the batch, and 0 / 1 / 2 for q / k / v.
+ * Call once with the five array pointers NULL to learn the sizes: *n_items items and *max_kv key tiles
+ * per item at most. Then pass device arrays q_got (n_items*2*128 int32), k_got and v_got
+ * (n_items*2*max_kv*128 int32 each) and host arrays q_want, k_want of the same sizes: the kernel
+ * writes the token ids it found (-1: a zero row, -2: the two halves of a row disagree, -4: wrong head
+ * or batch, -5: wrong tensor), the host side
+ * the ids the index maps of intra_index.h prescribe (-9: the row is never used). Returns
+ * INTRA_ERR_UNSUPPORTED for shapes the TMA path does not take, INTRA_ERR_KERNEL if a query row's key
+ * interval reaches a slot without a key. */
+int intra_b200_test_tma_rows(const void* q, const void* k, const void* v, int B, int S, int H, int Hkv,
+                             const int64_t q_strides[3], const int64_t k_strides[3],
+                             const int64_t v_strides[3], int family, int pattern, int param,
+                             int32_t* q_got_dev, int32_t* k_got_dev, int32_t* v_got_dev,
+                             int32_t* q_want, int32_t* k_want, int64_t* n_items, int64_t* max_kv,
+                             int device, void* cuda_stream);
+
+/* Test hook: overrides the launcher's choice of kernel variant for all later launches of the process:
+ * no_tma != 0 forces the cp.async row gathers, softmax_split 2 or 4 forces that column split;
+ * (0, 0) restores the launcher's own choice. Replaces nothing in the reference. */
+int intra_b200_test_force_path(int no_tma, int softmax_split);
+
+/* Test hooks for the failure path (the reference has none). _poke_status synchronises the device and
+ * overwrites its status word from the host. _wait_timeout launches a two-warp kernel in which one
+ * warp's wait is never satisfied and runs out after limit_ms (1..1000); it returns normally, leaves
+ * 100 + 92 in the status word, and writes to *waited_ns_dev how long the OTHER warp, whose own limit
+ * is the attention kernel's two seconds, waited before the first warp's give-up released it. */
+int intra_b200_test_poke_status(int device, int value);
+int intra_b200_test_wait_timeout(int limit_ms, long long* waited_ns_dev, int device, void* cuda_stream);
+
 /* intra_b200_fwd_llm for hosts that cannot let a library allocate device memory. It has no
  * counterpart in the reference.
  *
@@ -119,7 +167,8 @@ int intra_b200_selftest_umma(const void* a, const void* b, const void* v, float 
  * start-up leaves nothing for a cudaMalloc made later from inside a library, and a latency-bound
  * serving thread cannot afford the device-wide synchronisation a cudaMalloc implies. The regular
  * entry points allocate once per device (a status word the kernel reports to); this one never calls
- * cudaMalloc, cudaFree or any other allocating routine. The caller still passes q, k, v and out.
+ * cudaMalloc, cudaFree or any other allocating routine, and runs the same kernel. The caller still
+ * passes q, k, v and out.
  *
  * The kernel's scratch - today that one status word - lives in a fixed 256-byte array that is part of
  * the library image, so every GPU that loads the library carries those 256 bytes until the process
@@ -129,12 +178,15 @@ int intra_b200_selftest_umma(const void* a, const void* b, const void* v, float 
  * intra_b200_fwd_llm.
  *
  * The first call on a device looks up the array's device address (with that device made current)
- * and opts the kernel into its shared-memory size; make that first call before any stream capture.
+ * and opts the kernels into their shared-memory size; make that first call before any stream capture.
  * Every call on a device shares the array: the call clears the status word on `cuda_stream` before
  * its launch, so calls whose GPU work overlaps (different streams, or threads racing on one device)
- * race on that word - serialise them on one stream. The array keeps what the last call left: pass a
- * non-null `prev_status` to have the call first synchronise `cuda_stream` and copy out the word left
- * by the previous call (0 = healthy, also before the first call); pass NULL to stay asynchronous. */
+ * race on that word - serialise them on one stream. The array keeps what the last call left, and that
+ * is the only way to learn whether a call's kernel gave up: pass a non-null `prev_status` to have the
+ * NEXT call first synchronise `cuda_stream` and copy out the word the previous call left (0 = healthy,
+ * also before the first call); with NULL the call stays asynchronous and the previous call's word is
+ * cleared unread. `prev_status` is written only when the arguments pass validation; on an argument
+ * error it is left untouched. intra_b200_device_status does not see this array (and would allocate). */
 int intra_b200_fwd_llm_noalloc(const void* q, const void* k, const void* v, void* out,
                                int B, int S, int H, int Hkv,
                                const int64_t q_strides[3], const int64_t k_strides[3],

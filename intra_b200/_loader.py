@@ -37,6 +37,13 @@ SIGNATURES = {
     "intra_b200_visited_device": (_i, [_i, _i, _i, _i, _vp, _i, _vp]),
     "intra_b200_tile_counts": (_i, [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]),
     "intra_b200_selftest_umma": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _i, _vp]),
+    "intra_b200_test_tma_rows": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _I64x3, _I64x3, _I64x3, _i, _i, _i,
+                                      _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(ctypes.c_int64),
+                                      ctypes.POINTER(ctypes.c_int64), _i, _vp]),
+    "intra_b200_interleave_heads": (_i, [_vp, _vp, _i, ctypes.c_int64, ctypes.c_int64, _i, _vp]),
+    "intra_b200_test_force_path": (_i, [_i, _i]),
+    "intra_b200_test_poke_status": (_i, [_i, _i]),
+    "intra_b200_test_wait_timeout": (_i, [_i, _vp, _i, _vp]),
 }
 
 

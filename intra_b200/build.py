@@ -18,7 +18,8 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libintra_b200.so")
 SOURCES = [os.path.join(CSRC, "capi.cu")]
-HEADERS = [os.path.join(CSRC, f) for f in ("attn_kernel.cuh", "attn_kernel_dual.cuh", "intra_index.h", "ptx.cuh", "selftest.cuh", "tma_maps.h")] + [
+# every header next to the sources counts: an edit to any of them must trigger a rebuild
+HEADERS = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) + [
     os.path.join(PKG_DIR, "..", "include", "intra_b200.h")]
 
 

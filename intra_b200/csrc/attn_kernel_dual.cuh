@@ -35,23 +35,6 @@
 
 namespace intra {
 
-// Optional cycle-stamp tracing of CTA 0's first item (built only with -DINTRA_TRACE, for bring-up):
-// trace[(role * 64 + (iteration & 63)) * 8 + event] = clock64().
-#ifdef INTRA_TRACE
-__device__ long long g_trace[4 * 64 * 8];
-__device__ long long g_trace_item[4 * 32 * 8];
-#ifndef INTRA_TRACE_SEQ
-#define INTRA_TRACE_SEQ 0
-#endif
-#define INTRA_TRACE_EV(cond, role, iter, ev) \
-  do { if ((cond) && blockIdx.x == 0 && seq == INTRA_TRACE_SEQ && (iter) < 64) g_trace[((role) * 64 + (iter)) * 8 + (ev)] = clock64(); } while (0)
-#define INTRA_TRACE_ITEM(cond, role, ev) \
-  do { if ((cond) && blockIdx.x == 0 && seq < 32) g_trace_item[((role) * 32 + seq) * 8 + (ev)] = clock64(); } while (0)
-#else
-#define INTRA_TRACE_EV(cond, role, iter, ev) do {} while (0)
-#define INTRA_TRACE_ITEM(cond, role, ev) do {} while (0)
-#endif
-
 // Softmax column split: each query row of a sub-tile is shared by NSPLIT threads (one per softmax
 // warpgroup), 128 / NSPLIT score columns each. Two instantiations: NSPLIT = 4 (768 threads) hides more
 // latency and wins on short items, NSPLIT = 2 (512 threads) leaves the MMA-issuing warp's scheduler
@@ -158,11 +141,11 @@ struct DualItem {
 };
 
 // Item number `seq` of this CTA: heaviest-first list dealt round by round, every other round reversed.
-__device__ __forceinline__ int dual_item_index(int seq, int cta, int n_cta) {
+INTRA_HD int dual_item_index(int seq, int cta, int n_cta) {
   return seq * n_cta + ((seq & 1) ? (n_cta - 1 - cta) : cta);
 }
 
-__device__ __forceinline__ DualItem dual_decode(const DualParams& p, int item) {
+INTRA_HD DualItem dual_decode(const DualParams& p, int item) {
   DualItem it;
   const int per_tile = p.f.B * p.heads_per_item;
   const int idx = item / per_tile;
@@ -270,6 +253,21 @@ __device__ __forceinline__ void plan_query(const Problem& prob, const Tile& t, i
   *is_text = tma_box_coords(prob, t, start, text, head, batch, c);
   *rank4 = *is_text || t.kind == KIND_LLM_WINDOW;
 }
+// TMA box coordinates of an item's two query tiles and of its key tiles (shared-key modes), for the
+// thread that issues the loads.
+__device__ __forceinline__ void plan_slot_boxes(const DualParams& p, const DualItem& di, ItemSlot& sl) {
+  const int n_kv = di.pt.kv.n_kv_tiles;
+  const bool image_kind = di.pt.kv.kind == KIND_IMG_SCATTER;
+  const int n_text = image_kind && TEXT_LEN / TILE_N < n_kv ? TEXT_LEN / TILE_N : n_kv;
+  sl.n_text = n_text;
+  kv_segment(p.f.prob, di.pt.kv, 0, n_text, di.hk, di.b, &sl.seg0);
+  if (n_text < n_kv) kv_segment(p.f.prob, di.pt.kv, n_text, n_kv, di.hk, di.b, &sl.seg1);
+  // an absent sub-tile (odd tile count) is fed the other one's rows; its results are dropped
+  const Tile& t0 = di.pt.sub[0].n_kv_tiles > 0 ? di.pt.sub[0] : di.pt.sub[1];
+  const Tile& t1 = di.pt.sub[1].n_kv_tiles > 0 ? di.pt.sub[1] : di.pt.sub[0];
+  plan_query(p.f.prob, t0, di.h0, di.b, sl.q0, &sl.q0_text, &sl.q0_rank4);
+  plan_query(p.f.prob, t1, di.h1, di.b, sl.q1, &sl.q1_text, &sl.q1_rank4);
+}
 // Planner warp: fills ring slot after ring slot with the CTA's non-empty items, then one end marker.
 // slot_ready[r] completes once per fill of slot r; slot_free[r] once all consumers have let go of it.
 __device__ __forceinline__ void plan_items(const DualParams& p, ItemSlot* ring, uint64_t* slot_ready, uint64_t* slot_free,
@@ -310,18 +308,7 @@ __device__ __forceinline__ void plan_items(const DualParams& p, ItemSlot* ring, 
         sl.n_kv = n_kv;
         sl.b = di.b; sl.h0 = di.h0; sl.h1 = di.h1; sl.hk = di.hk;
         sl.pt = di.pt;
-        if (plan_boxes) {
-          const bool image_kind = di.pt.kv.kind == KIND_IMG_SCATTER;
-          const int n_text = image_kind && TEXT_LEN / TILE_N < n_kv ? TEXT_LEN / TILE_N : n_kv;
-          sl.n_text = n_text;
-          kv_segment(p.f.prob, di.pt.kv, 0, n_text, di.hk, di.b, &sl.seg0);
-          if (n_text < n_kv) kv_segment(p.f.prob, di.pt.kv, n_text, n_kv, di.hk, di.b, &sl.seg1);
-          // an absent sub-tile (odd tile count) is fed the other one's rows; its results are dropped
-          const Tile& t0 = di.pt.sub[0].n_kv_tiles > 0 ? di.pt.sub[0] : di.pt.sub[1];
-          const Tile& t1 = di.pt.sub[1].n_kv_tiles > 0 ? di.pt.sub[1] : di.pt.sub[0];
-          plan_query(p.f.prob, t0, di.h0, di.b, sl.q0, &sl.q0_text, &sl.q0_rank4);
-          plan_query(p.f.prob, t1, di.h1, di.b, sl.q1, &sl.q1_text, &sl.q1_rank4);
-        }
+        if (plan_boxes) plan_slot_boxes(p, di, sl);
       }
     }
     __syncwarp();
@@ -466,11 +453,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
-  if (tid == 0) abort_flag = *reinterpret_cast<volatile int*>(p.f.status);
-  __syncthreads();
-  if (abort_flag != 0) return;                          // an earlier launch or CTA already failed
-  __syncthreads();
-
   uint64_t* q_full = &bars[0];       // Q of sub-tile 0 has landed
   uint64_t* q1_full = &bars[17];     // Q of sub-tile 1 has landed
   uint64_t* k_full = &bars[1];
@@ -503,11 +485,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     ptx::mbar_init(s0_full, 1);
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&s1_full[s], 1);
-#ifdef INTRA_PFULL_PER_THREAD
-      ptx::mbar_init(&p_full[s], SM_THREADS);
-#else
       ptx::mbar_init(&p_full[s], SM_WARPS);               // one arrival per softmax warp
-#endif
       ptx::mbar_init(&o_done[s], 1);
     }
     ptx::mbar_init(drain, 1);
@@ -576,7 +554,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       const int token[2] = {sl.token[0][row], sl.token[1][row]};
       const int item_b = sl.b, item_h[2] = {sl.h0, sl.h1};
       INTRA_RING_RELEASE_WARP();
-      INTRA_TRACE_ITEM(tid == 0, 1, 0);
       float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};    // running maxima (identical in both halves)
       float l_part[2] = {0.f, 0.f};                       // this half's share of the row sums
 
@@ -587,7 +564,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           else ok = ptx::mbar_wait(&s1_full[it & 1], (it >> 1) & 1, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 11 + sx; break; }
           ptx::tc_fence_after();
-          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 0);
           const uint32_t s_addr = lane_addr + sx * 128;
           const uint32_t o_addr = lane_addr + 256 + sx * 128 + half * COLS;
 
@@ -596,7 +572,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           for (int c = 0; c < COLS / 32; ++c)
             ptx::tmem_ld32(s_addr + half * COLS + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
           ptx::tmem_wait_ld();
-          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 1);
 
           const int u0 = n * TILE_N + half * COLS;
           // Rows whose key interval does not cover these columns (diagonal and window-edge tiles) mask
@@ -622,7 +597,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             }
           }
           const float my_max = sm::row_max(s);
-          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 5);
           xch_max[ph & 1][half][row] = my_max;
           __syncwarp();                                   // rendezvous of all 8 softmax warps (bounded, unlike
           if (lane == 0) ptx::mbar_arrive(xbar);          // bar.sync): one arrival per warp
@@ -633,7 +607,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           for (int o = 1; o < NSPLIT; ++o) tile_max = fmaxf(tile_max, xch_max[ph & 1][(half + o) % NSPLIT][row]);
           ++ph;
           const float m_new = fmaxf(m_run[sx], tile_max);
-          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 2);
           // Move the running maximum only when the scores outgrow it by 2^8; until then p is merely
           // scaled by a constant that the final division by the row sum removes.
           const bool grow = (m_new - m_run[sx]) * scale_log2 > RESCALE_THRESHOLD;
@@ -663,19 +636,12 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             uint32_t pk[16];
             sm::exp_chunk(s, c2 * 32, scale_log2, base, pk, sum);
             ptx::tmem_st16(s_addr + half * (COLS / 2) + c2 * 16, pk);
-            INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 6 + c2);
           }
           l_part[sx] += sm::sum4(sum);
-          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 3);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
-#ifdef INTRA_PFULL_PER_THREAD
-          ptx::mbar_arrive(&p_full[sx]);
-#else
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(&p_full[sx]);
-#endif
-          INTRA_TRACE_EV((tid & 127) == 0 && half == 0, 1 + sx, n, 4);
         }
       }
       if (!ok) break;
@@ -702,11 +668,9 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       ++ph;
 #pragma unroll
       for (int sx = 0; sx < 2; ++sx) {
-        INTRA_TRACE_ITEM(tid == 0, 1, 3 + 2 * sx);
         ok = ptx::mbar_wait(&o_done[sx], n_done & 1, abort_p);     // last PV of this item
         if (!ok) { if (*abort_p == 1) *abort_p = 15 + sx; break; }
         ptx::tc_fence_after();
-        INTRA_TRACE_ITEM(tid == 0, 1, 4 + 2 * sx);
         float l_tot = l_part[sx];
 #pragma unroll
         for (int o = 1; o < NSPLIT; ++o) l_tot += xch_sum[ipar][sx][(half + o) % NSPLIT][row];
@@ -722,7 +686,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       }
       if (!ok) break;
       ++n_done;
-      INTRA_TRACE_ITEM(tid == 0, 1, 2);
     }
   } else if (warp < SM_WARPS + 4) {
     // ================================ epilogue warps / loaders =====================================
@@ -745,13 +708,11 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
         const int ipar = n_done & 1;
         ok = ptx::mbar_wait(l_ready, ipar, abort_p);
         if (!ok) { if (*abort_p == 1) *abort_p = 41; break; }
-        INTRA_TRACE_ITEM(lt == 0, 2, 0);
 #pragma unroll
         for (int sx = 0; sx < 2; ++sx) {
           ok = ptx::mbar_wait(&o_done[sx], ipar, abort_p);         // last PV of this item
           if (!ok) { if (*abort_p == 1) *abort_p = 42 + sx; break; }
           ptx::tc_fence_after();
-          INTRA_TRACE_ITEM(lt == 0, 2, 1 + 2 * sx);
           float l_tot = 0.f;
 #pragma unroll
           for (int o = 0; o < NSPLIT; ++o) l_tot += xch_sum[ipar][sx][o][row];
@@ -764,7 +725,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           store_o_row(lane_addr + 256 + sx * 128, 128, inv, dst, tk >= 0, p.wide_stores != 0);
           ptx::tc_fence_before();
           ptx::mbar_arrive(&o_free[sx]);                           // the next item's first PV may overwrite O
-          INTRA_TRACE_ITEM(lt == 0, 2, 2 + 2 * sx);
         }
         ++n_done;
       }
@@ -872,10 +832,8 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             INTRA_WAIT_TILE_DONE(kc - 2, 22);
             if (!ok) break;
           }
-          INTRA_TRACE_EV(true, 3, n, 0);
           ptx::mbar_arrive_expect_tx(&k_full[stage], TILE_BYTES);
           tma_fetch_planned(sg, n, kmap, k_smem0 + stage * TILE_BYTES, &k_full[stage]);
-          INTRA_TRACE_EV(true, 3, n, 1);
           if (n == 0) {
             // The item's queries go in between its first K and V tiles, each as early as its buffer
             // frees: Q0 after QK0 of the previous item's last key tile, Q1 after that tile's QK1.
@@ -883,7 +841,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
               ok = ptx::mbar_wait(s0_full, (kc - 1) & 1, abort_p);
               if (!ok) { if (*abort_p == 1) *abort_p = 21; break; }
             }
-            INTRA_TRACE_ITEM(true, 3, 0);
             ptx::mbar_arrive_expect_tx(q_full, TILE_BYTES);
             tma_fetch_box(sl.q0, sl.q0_rank4, sl.q0_text ? q_op.text_map : q_op.main_map, q_smem0, q_full);
           }
@@ -895,10 +852,8 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             ptx::mbar_arrive_expect_tx(q1_full, TILE_BYTES);
             tma_fetch_box(sl.q1, sl.q1_rank4, sl.q1_text ? q_op.text_map : q_op.main_map, q_smem0 + TILE_BYTES, q1_full);
           }
-          INTRA_TRACE_EV(true, 3, n, 2);
           ptx::mbar_arrive_expect_tx(&v_full[stage], TILE_BYTES);
           tma_fetch_planned(sg, n, vmap, v_smem0 + stage * TILE_BYTES, &v_full[stage]);
-          INTRA_TRACE_EV(true, 3, n, 3);
         }
         if (!ok) break;
         ptx::mbar_arrive(&slot_free[seq % ITEM_RING]);
@@ -925,10 +880,8 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
         INTRA_RING_ACQUIRE(sl, 56);
         const int n_kv = sl.n_kv;
         INTRA_RING_RELEASE_WARP();
-        INTRA_TRACE_ITEM(lane == 0, 0, 0);
         ok = ptx::mbar_wait(q_full, n_done & 1, abort_p);
         if (!ok) { if (*abort_p == 1) *abort_p = 31; break; }
-        INTRA_TRACE_ITEM(lane == 0, 0, 1);
         for (int n = 0; n < n_kv; ++n, ++kc) {
           // shared keys: both sub-tiles read ring stage kc % 2; split keys: sub-tile s reads buffer s
           const int stage = kSplitKV ? 0 : kc % KV_STAGES;
@@ -937,7 +890,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           if (!ok) { if (*abort_p == 1) *abort_p = 32; break; }
           ptx::fence_proxy_async_smem();
           ptx::tc_fence_after();
-          INTRA_TRACE_EV(lane == 0, 0, n, 0);
           const uint64_t k_desc = k_desc0 + stage * kStageStep;
           if (ptx::elect_one()) {
             issue_qk_desc(q0_desc, k_desc, tmem + 0);
@@ -957,7 +909,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
               ptx::fence_proxy_async_smem();
             }
             ptx::tc_fence_after();
-            INTRA_TRACE_EV(lane == 0, 0, n, 1);
             if (ptx::elect_one()) {
               issue_pv_desc(tmem + 128, v_desc0 + pend_stage * kStageStep, tmem + 384, pend_acc != 0);
               if (pend_last) ptx::mma_commit(&o_done[1]);
@@ -983,11 +934,9 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             ptx::mma_commit(&s1_full[kc & 1]);
           }
           __syncwarp();
-          INTRA_TRACE_EV(lane == 0, 0, n, 2);
           ok = ptx::mbar_wait(&v_full[stage], par, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 34; break; }
           ptx::fence_proxy_async_smem();
-          INTRA_TRACE_EV(lane == 0, 0, n, 3);
           ok = ptx::mbar_wait(&p_full[0], it0 & 1, abort_p);
           if (!ok) { if (*abort_p == 1) *abort_p = 35; break; }
           if (n == 0 && n_done > 0) {                     // O0 of the previous item must have been read
@@ -995,13 +944,11 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             if (!ok) { if (*abort_p == 1) *abort_p = 37; break; }
           }
           ptx::tc_fence_after();
-          INTRA_TRACE_EV(lane == 0, 0, n, 4);
           if (ptx::elect_one()) {
             issue_pv_desc(tmem + 0, v_desc0 + stage * kStageStep, tmem + 256, n > 0);
             if (n == n_kv - 1) ptx::mma_commit(&o_done[0]);
           }
           __syncwarp();
-          INTRA_TRACE_EV(lane == 0, 0, n, 5);
           ++it0;
           pend = true;
           pend_last = (n == n_kv - 1);
@@ -1009,7 +956,6 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           pend_stage = kSplitKV ? 1 : stage;
           pend_item = n_done;
         }
-        INTRA_TRACE_ITEM(lane == 0, 0, 2);
         ++n_done;
       }
       if (ok && pend) {

@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <mutex>
@@ -14,6 +15,7 @@
 
 #include "attn_kernel.cuh"
 #include "attn_kernel_dual.cuh"
+#include "gather_kernel.cuh"
 #include "selftest.cuh"
 
 namespace {
@@ -30,6 +32,10 @@ struct DeviceState {
   int sm_count = 0;
 };
 DeviceState g_dev[MAX_DEVICES];
+
+// Test hook (intra_b200_test_force_path): overrides of the launcher's own choice of kernel variant.
+std::atomic<int> g_force_no_tma{0};      // 1: cp.async row gathers even where TMA boxes would do
+std::atomic<int> g_force_split{0};       // 2 or 4: softmax column split; 0: the launcher decides
 
 int cuda_fail(cudaError_t e) {
   g_last_cuda_error = static_cast<int>(e);
@@ -49,6 +55,24 @@ struct DeviceGuard {
   }
 };
 
+// Shared-memory opt-in of every kernel variant, on the current device. Allocates nothing.
+template <typename K>
+cudaError_t opt_in_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+cudaError_t set_kernel_attributes() {
+  cudaError_t e = opt_in_smem(umma_selftest_kernel, SELFTEST_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<2, false, true>, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<2, false, false>, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<4, false, true>, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<4, false, false>, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<2, true, true>, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<2, true, false>, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<4, true, true>, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<4, true, false>, DUAL_SMEM_BYTES);
+  return e;
+}
+
 // One-time set-up of a device (current when called): architecture check, shared-memory opt-in of the
 // kernels, and the status word the kernels report to.
 void init_device(int device) {
@@ -57,28 +81,7 @@ void init_device(int device) {
   cudaError_t e = cudaGetDeviceProperties(&prop, device);
   if (e != cudaSuccess) { st.init_status = cuda_fail(e); return; }
   if (prop.major != 10) { st.init_status = INTRA_ERR_DEVICE; return; }
-  e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                             cudaSharedmemCarveoutMaxShared);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<2, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_dual_kernel<4, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);
+  e = set_kernel_attributes();
   st.sm_count = prop.multiProcessorCount;
   if (e == cudaSuccess) e = cudaMalloc(&st.status_word, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(st.status_word, 0, sizeof(int));
@@ -224,6 +227,7 @@ struct NoAllocState {
   std::once_flag once;
   int init_status = INTRA_OK;
   int* scratch = nullptr;         // device address of g_noalloc_scratch on this device
+  int sm_count = 0;
 };
 NoAllocState g_noalloc[MAX_DEVICES];
 
@@ -234,10 +238,8 @@ void init_noalloc(int device) {
   cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
   if (e != cudaSuccess) { st.init_status = cuda_fail(e); return; }
   if (major != 10) { st.init_status = INTRA_ERR_DEVICE; return; }
-  e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                             cudaSharedmemCarveoutMaxShared);
+  e = cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (e == cudaSuccess) e = set_kernel_attributes();
   void* ptr = nullptr;
   if (e == cudaSuccess) e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
   if (e != cudaSuccess) { st.init_status = cuda_fail(e); return; }
@@ -247,26 +249,61 @@ void init_noalloc(int device) {
 // Bytes of scratch one launch of the attention kernel needs: its status word.
 size_t fwd_scratch_bytes(const Problem&) { return sizeof(int); }
 
-int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, int S, int H, int Hkv,
+// Checks that need no device: pointers, sizes, alignment, and the pattern's problem description.
+int check_args(const void* q, const void* k, const void* v, void* out, int B, int S, int H, int Hkv,
                const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, int family, int pattern,
-               int param, float softmax_scale, int device, void* stream, float* lse = nullptr) {
+               int param, float softmax_scale, Problem* prob) {
   if (!q || !k || !v || !out || B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0) return INTRA_ERR_BAD_ARG;
   if (!qs || !ks || !vs || !os) return INTRA_ERR_BAD_ARG;
   if (!(softmax_scale > 0.f) || !std::isfinite(softmax_scale)) return INTRA_ERR_BAD_ARG;
+  // every head, token and batch of the output must be a distinct row: a zero or negative stride (an
+  // expanded tensor) would make different tiles write the same memory
+  if (os[0] <= 0 || os[1] <= 0 || os[2] <= 0) return INTRA_ERR_BAD_ARG;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !strides_ok(qs) || !strides_ok(ks) ||
       !strides_ok(vs) || !strides_ok(os))
     return INTRA_ERR_ALIGNMENT;
-  FwdParams p;
-  int rc = problem_from(family, pattern, S, param, &p.prob);
+  int rc = problem_from(family, pattern, S, param, prob);
   if (rc != INTRA_OK) return rc;
-  const int64_t blocks = int64_t(p.prob.n_tiles) * B * H;
+  const int64_t blocks = int64_t(prob->n_tiles) * B * H;
   if (blocks <= 0 || blocks > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
+  return INTRA_OK;
+}
 
-  DeviceGuard guard(device);
-  if (!guard.ok) return cuda_fail(cudaGetLastError());
-  rc = ensure_device(device);
-  if (rc != INTRA_OK) return rc;
+// How the launcher splits a problem into the persistent kernel's items, and which kernel variant it
+// picks (the counterpart of the reference's MASK_SWITCH / launch templates,
+// csrc/flash_attn/src/flash_fwd_launch_template.h:401-565, :720-776).
+int plan_launch(const FwdParams& p, DualParams* d, bool* four) {
+  d->f = p;
+  d->split_kv = p.prob.kind == KIND_IMG_GATHER0 ? 1 : 0;
+  d->row_pairs = (d->split_kv || (p.H / p.Hkv) % 2 != 0) ? 1 : 0;
+  d->n_pair_tiles = n_pair_tiles(p.prob, d->row_pairs);
+  d->heads_per_item = d->row_pairs ? p.H : p.H / 2;
+  const int64_t items = int64_t(d->n_pair_tiles) * p.B * d->heads_per_item;
+  if (items <= 0 || items > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
+  d->n_items = static_cast<int>(items);
+  d->wide_stores = (reinterpret_cast<uintptr_t>(p.o) % 32 == 0 && p.os.sb % 16 == 0 && p.os.ss % 16 == 0 && p.os.sh % 16 == 0) ? 1 : 0;
+  d->use_tma = !g_force_no_tma.load() && tma_supported(p.prob) &&
+               build_maps(p.prob, p.q, p.qs, p.H, p.B, true, &d->maps.q_main, &d->maps.q_text, &d->maps.k_aux) &&
+               build_maps(p.prob, p.k, p.ks, p.Hkv, p.B, false, &d->maps.k_main, &d->maps.k_text, &d->maps.k_aux) &&
+               build_maps(p.prob, p.v, p.vs, p.Hkv, p.B, false, &d->maps.v_main, &d->maps.v_text, &d->maps.v_aux);
+  // Softmax column split (attn_kernel_dual.cuh): 4-way for short items, 2-way for long ones.
+  int64_t n_tiles = 0, n_kv = 0;
+  for (int idx = 0; idx < d->n_pair_tiles; ++idx) {
+    const int t = make_pair(p.prob, d->row_pairs, idx).kv.n_kv_tiles;
+    if (t > 0) { ++n_tiles; n_kv += t; }
+  }
+  const int force_split = g_force_split.load();
+  *four = force_split ? force_split == 4 : (n_tiles > 0 && n_kv < 24 * n_tiles);
+  return INTRA_OK;
+}
 
+// Fills the parameter block and launches the attention kernel on `stream` of the current device.
+// `status_word` is where the kernel records a bounded wait that ran out; nothing here allocates.
+int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, int H, int Hkv, const int64_t* qs,
+               const int64_t* ks, const int64_t* vs, const int64_t* os, const Problem& prob, float softmax_scale,
+               int* status_word, int sm_count, cudaStream_t st, float* lse) {
+  FwdParams p;
+  p.prob = prob;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k = static_cast<const __nv_bfloat16*>(k);
   p.v = static_cast<const __nv_bfloat16*>(v);
@@ -277,53 +314,41 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
   p.os = {os[0], os[1], os[2]};
   p.B = B; p.H = H; p.Hkv = Hkv;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
-  p.status = g_dev[device].status_word;
+  p.status = status_word;
   p.lse = lse;
-  // Everything runs on the persistent two-sub-tile kernel (Gather-0, whose tiles share no keys, with one
-  // K / V buffer per sub-tile); INTRA_B200_SINGLE_TILE=1 forces the one-tile kernel, for A/B runs.
-  static const bool force_single = [] { const char* v = std::getenv("INTRA_B200_SINGLE_TILE"); return v && v[0] == '1'; }();
-  if (!force_single) {
-    DualParams d;
-    d.f = p;
-    d.split_kv = p.prob.kind == KIND_IMG_GATHER0 ? 1 : 0;
-    d.row_pairs = (d.split_kv || (H / Hkv) % 2 != 0) ? 1 : 0;
-    d.n_pair_tiles = n_pair_tiles(p.prob, d.row_pairs);
-    d.heads_per_item = d.row_pairs ? H : H / 2;
-    const int64_t items = int64_t(d.n_pair_tiles) * B * d.heads_per_item;
-    if (items <= 0 || items > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
-    d.n_items = static_cast<int>(items);
-    static const bool no_tma = [] { const char* v = std::getenv("INTRA_B200_NO_TMA"); return v && v[0] == '1'; }();
-    d.wide_stores = (reinterpret_cast<uintptr_t>(out) % 32 == 0 && os[0] % 16 == 0 && os[1] % 16 == 0 && os[2] % 16 == 0) ? 1 : 0;
-    d.use_tma = !no_tma && tma_supported(p.prob) &&
-                build_maps(p.prob, p.q, p.qs, H, B, true, &d.maps.q_main, &d.maps.q_text, &d.maps.k_aux) &&
-                build_maps(p.prob, p.k, p.ks, Hkv, B, false, &d.maps.k_main, &d.maps.k_text, &d.maps.k_aux) &&
-                build_maps(p.prob, p.v, p.vs, Hkv, B, false, &d.maps.v_main, &d.maps.v_text, &d.maps.v_aux);
-    const int grid = static_cast<int>(items < g_dev[device].sm_count ? items : g_dev[device].sm_count);
-    // Softmax column split (attn_kernel_dual.cuh): 4-way for short items, 2-way for long ones.
-    int64_t n_tiles = 0, n_kv = 0;
-    for (int idx = 0; idx < d.n_pair_tiles; ++idx) {
-      const int t = make_pair(p.prob, d.row_pairs, idx).kv.n_kv_tiles;
-      if (t > 0) { ++n_tiles; n_kv += t; }
-    }
-    static const int force_split = [] { const char* v = std::getenv("INTRA_B200_SOFTMAX_SPLIT"); return v ? std::atoi(v) : 0; }();
-    const bool four = force_split ? force_split == 4 : (n_tiles > 0 && n_kv < 24 * n_tiles);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DualParams d;
+  bool four = false;
+  int rc = plan_launch(p, &d, &four);
+  if (rc != INTRA_OK) return rc;
+  const int grid = d.n_items < sm_count ? d.n_items : sm_count;     // persistent: one CTA per SM
 #define INTRA_LAUNCH_DUAL(N, SPLIT) \
-    do { \
-      if (d.use_tma) intra_fwd_dual_kernel<N, SPLIT, true><<<grid, DualCfg<N>::THREADS, DUAL_SMEM_BYTES, st>>>(d); \
-      else intra_fwd_dual_kernel<N, SPLIT, false><<<grid, DualCfg<N>::THREADS, DUAL_SMEM_BYTES, st>>>(d); \
-    } while (0)
-    if (four && d.split_kv) INTRA_LAUNCH_DUAL(4, true);
-    else if (four) INTRA_LAUNCH_DUAL(4, false);
-    else if (d.split_kv) INTRA_LAUNCH_DUAL(2, true);
-    else INTRA_LAUNCH_DUAL(2, false);
+  do { \
+    if (d.use_tma) intra_fwd_dual_kernel<N, SPLIT, true><<<grid, DualCfg<N>::THREADS, DUAL_SMEM_BYTES, st>>>(d); \
+    else intra_fwd_dual_kernel<N, SPLIT, false><<<grid, DualCfg<N>::THREADS, DUAL_SMEM_BYTES, st>>>(d); \
+  } while (0)
+  if (four && d.split_kv) INTRA_LAUNCH_DUAL(4, true);
+  else if (four) INTRA_LAUNCH_DUAL(4, false);
+  else if (d.split_kv) INTRA_LAUNCH_DUAL(2, true);
+  else INTRA_LAUNCH_DUAL(2, false);
 #undef INTRA_LAUNCH_DUAL
-  } else {
-    intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
-  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return INTRA_OK;
+}
+
+// The regular entry points: per-device state (with its one allocation, the status word) on first use.
+int run_fwd(const void* q, const void* k, const void* v, void* out, int B, int S, int H, int Hkv,
+            const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, int family, int pattern,
+            int param, float softmax_scale, int device, void* stream, float* lse = nullptr) {
+  Problem prob;
+  int rc = check_args(q, k, v, out, B, S, H, Hkv, qs, ks, vs, os, family, pattern, param, softmax_scale, &prob);
+  if (rc != INTRA_OK) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  rc = ensure_device(device);
+  if (rc != INTRA_OK) return rc;
+  return launch_fwd(q, k, v, out, B, H, Hkv, qs, ks, vs, os, prob, softmax_scale, g_dev[device].status_word,
+                    g_dev[device].sm_count, static_cast<cudaStream_t>(stream), lse);
 }
 
 }  // namespace
@@ -335,7 +360,7 @@ int intra_b200_fwd_llm(const void* q, const void* k, const void* v, void* out, i
                        const int64_t out_strides[3], int pattern, int group_num, int window, float softmax_scale,
                        int device, void* cuda_stream) {
   const int param = pattern == INTRA_LLM_WINDOW ? window : group_num;
-  return launch_fwd(q, k, v, out, B, S, H, Hkv, q_strides, k_strides, v_strides, out_strides, 0, pattern, param,
+  return run_fwd(q, k, v, out, B, S, H, Hkv, q_strides, k_strides, v_strides, out_strides, 0, pattern, param,
                     softmax_scale, device, cuda_stream);
 }
 
@@ -343,7 +368,7 @@ int intra_b200_fwd_image(const void* q, const void* k, const void* v, void* out,
                          const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                          const int64_t out_strides[3], int pattern, int width, float softmax_scale, int device,
                          void* cuda_stream) {
-  return launch_fwd(q, k, v, out, B, S, H, H, q_strides, k_strides, v_strides, out_strides, 1, pattern, width,
+  return run_fwd(q, k, v, out, B, S, H, H, q_strides, k_strides, v_strides, out_strides, 1, pattern, width,
                     softmax_scale, device, cuda_stream);
 }
 
@@ -353,7 +378,7 @@ int intra_b200_fwd_llm_lse(const void* q, const void* k, const void* v, void* ou
                            int window, float softmax_scale, int device, void* cuda_stream) {
   if (!lse || reinterpret_cast<uintptr_t>(lse) % 4 != 0) return INTRA_ERR_BAD_ARG;
   const int param = pattern == INTRA_LLM_WINDOW ? window : group_num;
-  return launch_fwd(q, k, v, out, B, S, H, Hkv, q_strides, k_strides, v_strides, out_strides, 0, pattern, param,
+  return run_fwd(q, k, v, out, B, S, H, Hkv, q_strides, k_strides, v_strides, out_strides, 0, pattern, param,
                     softmax_scale, device, cuda_stream, lse);
 }
 
@@ -362,7 +387,7 @@ int intra_b200_fwd_image_lse(const void* q, const void* k, const void* v, void* 
                              const int64_t out_strides[3], int pattern, int width, float softmax_scale, int device,
                              void* cuda_stream) {
   if (!lse || reinterpret_cast<uintptr_t>(lse) % 4 != 0) return INTRA_ERR_BAD_ARG;
-  return launch_fwd(q, k, v, out, B, S, H, H, q_strides, k_strides, v_strides, out_strides, 1, pattern, width,
+  return run_fwd(q, k, v, out, B, S, H, H, q_strides, k_strides, v_strides, out_strides, 1, pattern, width,
                     softmax_scale, device, cuda_stream, lse);
 }
 
@@ -488,9 +513,134 @@ int intra_b200_selftest_umma(const void* a, const void* b, const void* v, float 
   if (!guard.ok) return cuda_fail(cudaGetLastError());
   int rc = ensure_device(device);
   if (rc != INTRA_OK) return rc;
-  umma_selftest_kernel<<<1, 128, FWD_SMEM_BYTES, static_cast<cudaStream_t>(cuda_stream)>>>(
+  umma_selftest_kernel<<<1, 128, SELFTEST_SMEM_BYTES, static_cast<cudaStream_t>(cuda_stream)>>>(
       static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
       static_cast<const __nv_bfloat16*>(v), p_scale, s_out, o_out, g_dev[device].status_word);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
+}
+
+int intra_b200_interleave_heads(const void* parts, void* out, int world, int64_t rows, int64_t block_bytes,
+                                int device, void* cuda_stream) {
+  if (!parts || !out || world <= 0 || rows <= 0 || block_bytes <= 0) return INTRA_ERR_BAD_ARG;
+  if (!aligned16(parts) || !aligned16(out) || block_bytes % 16 != 0) return INTRA_ERR_ALIGNMENT;
+  if (block_bytes / 16 > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  int rc = ensure_device(device);
+  if (rc != INTRA_OK) return rc;
+  const int64_t total = int64_t(world) * rows * (block_bytes / 16);
+  const int64_t per_cta = int64_t(INTERLEAVE_THREADS) * INTERLEAVE_UNROLL;
+  const int64_t want = (total + per_cta - 1) / per_cta;
+  const int64_t cap = int64_t(g_dev[device].sm_count) * 8;           // 8 resident CTAs of 256 threads per SM
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  interleave_heads_kernel<<<grid, INTERLEAVE_THREADS, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint4*>(parts), static_cast<uint4*>(out), world, rows, static_cast<int>(block_bytes / 16));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
+}
+
+int intra_b200_test_force_path(int no_tma, int softmax_split) {
+  if (softmax_split != 0 && softmax_split != 2 && softmax_split != 4) return INTRA_ERR_BAD_ARG;
+  g_force_no_tma.store(no_tma ? 1 : 0);
+  g_force_split.store(softmax_split);
+  return INTRA_OK;
+}
+
+int intra_b200_test_poke_status(int device, int value) {
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  int rc = ensure_device(device);
+  if (rc != INTRA_OK) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(g_dev[device].status_word, &value, sizeof(int), cudaMemcpyHostToDevice);
+  return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
+}
+
+int intra_b200_test_wait_timeout(int limit_ms, long long* waited_ns_dev, int device, void* cuda_stream) {
+  if (limit_ms <= 0 || limit_ms > 1000 || !waited_ns_dev) return INTRA_ERR_BAD_ARG;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  int rc = ensure_device(device);
+  if (rc != INTRA_OK) return rc;
+  abort_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(cuda_stream)>>>(limit_ms, g_dev[device].status_word,
+                                                                             waited_ns_dev);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
+}
+
+int intra_b200_test_tma_rows(const void* q, const void* k, const void* v, int B, int S, int H, int Hkv,
+                             const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                             int family, int pattern, int param, int32_t* q_got_dev, int32_t* k_got_dev,
+                             int32_t* v_got_dev, int32_t* q_want, int32_t* k_want, int64_t* n_items, int64_t* max_kv,
+                             int device, void* cuda_stream) {
+  if (!n_items || !max_kv) return INTRA_ERR_BAD_ARG;
+  Problem prob;
+  // q doubles as the (unused) output pointer so that the common argument checks apply
+  int rc = check_args(q, k, v, const_cast<void*>(q), B, S, H, Hkv, q_strides, k_strides, v_strides, q_strides, family,
+                      pattern, param, 1.f, &prob);
+  if (rc != INTRA_OK) return rc;
+  if (!tma_supported(prob)) return INTRA_ERR_UNSUPPORTED;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError());
+  rc = ensure_device(device);
+  if (rc != INTRA_OK) return rc;
+  FwdParams p;
+  p.prob = prob;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k = static_cast<const __nv_bfloat16*>(k);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.o = nullptr;
+  p.qs = {q_strides[0], q_strides[1], q_strides[2]};
+  p.ks = {k_strides[0], k_strides[1], k_strides[2]};
+  p.vs = {v_strides[0], v_strides[1], v_strides[2]};
+  p.os = p.qs;
+  p.B = B; p.H = H; p.Hkv = Hkv;
+  p.scale_log2 = 1.f;
+  p.status = g_dev[device].status_word;
+  p.lse = nullptr;
+  DualParams d;
+  bool four = false;
+  const int forced = g_force_no_tma.exchange(0);           // the maps are wanted whatever the override says
+  rc = plan_launch(p, &d, &four);
+  g_force_no_tma.store(forced);
+  if (rc != INTRA_OK) return rc;
+  if (!d.use_tma) return INTRA_ERR_UNSUPPORTED;
+  int mk = 0;
+  for (int idx = 0; idx < d.n_pair_tiles; ++idx) mk = imax(mk, make_pair(prob, d.row_pairs, idx).kv.n_kv_tiles);
+  *n_items = d.n_items;
+  *max_kv = mk;
+  if (!q_got_dev || !k_got_dev || !v_got_dev || !q_want || !k_want) return INTRA_OK;     // sizes only
+
+  // what should arrive: -9 = any row will do (padding rows, slots no query attends)
+  for (int item = 0; item < d.n_items; ++item) {
+    const DualItem di = dual_decode(d, item);
+    for (int sx = 0; sx < 2; ++sx) {
+      int32_t* qw = q_want + (size_t(item) * 2 + sx) * TILE_M;
+      int32_t* kw = k_want + (size_t(item) * 2 + sx) * mk * TILE_N;
+      for (int i = 0; i < mk * TILE_N; ++i) kw[i] = -9;
+      for (int r = 0; r < TILE_M; ++r) qw[r] = -9;
+      if (di.pt.kv.n_kv_tiles == 0) continue;
+      const Tile& map = pair_kv_map(di.pt, d.split_kv, sx);
+      if (d.split_kv || sx == 0)
+        for (int u = 0; u < di.pt.kv.n_kv_tiles * TILE_N; ++u) {
+          const int kt = key_token(prob, map, u);
+          if (kt >= 0) kw[u] = kt;
+        }
+      for (int r = 0; r < TILE_M; ++r) {
+        int token, lo, hi;
+        pair_q_row(prob, di.pt, sx, r, &token, &lo, &hi);
+        if (token < 0) continue;
+        qw[r] = token;
+        // every attended slot must hold a real key: slots [0, nk) do, by key_token's first line
+        if (lo < 0 || hi >= map.nk || key_token(prob, map, lo) < 0 || key_token(prob, map, hi) < 0) return INTRA_ERR_KERNEL;
+      }
+    }
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  const int smem = TILE_BYTES + 1024;
+  if (d.split_kv) tma_rows_selftest_kernel<true><<<d.n_items, 128, smem, st>>>(d, q_got_dev, k_got_dev, v_got_dev, mk);
+  else tma_rows_selftest_kernel<false><<<d.n_items, 128, smem, st>>>(d, q_got_dev, k_got_dev, v_got_dev, mk);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
 }
@@ -499,20 +649,13 @@ int intra_b200_fwd_llm_noalloc(const void* q, const void* k, const void* v, void
                                const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                                const int64_t out_strides[3], int pattern, int group_num, int window,
                                float softmax_scale, int device, void* cuda_stream, int* prev_status) {
-  if (!q || !k || !v || !out || B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0) return INTRA_ERR_BAD_ARG;
-  if (!q_strides || !k_strides || !v_strides || !out_strides) return INTRA_ERR_BAD_ARG;
-  if (!(softmax_scale > 0.f) || !std::isfinite(softmax_scale)) return INTRA_ERR_BAD_ARG;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !strides_ok(q_strides) ||
-      !strides_ok(k_strides) || !strides_ok(v_strides) || !strides_ok(out_strides))
-    return INTRA_ERR_ALIGNMENT;
-  if (device < 0 || device >= MAX_DEVICES) return INTRA_ERR_BAD_ARG;
-  FwdParams p;
-  int rc = problem_from(0, pattern, S, pattern == INTRA_LLM_WINDOW ? window : group_num, &p.prob);
+  Problem prob;
+  int rc = check_args(q, k, v, out, B, S, H, Hkv, q_strides, k_strides, v_strides, out_strides, 0, pattern,
+                      pattern == INTRA_LLM_WINDOW ? window : group_num, softmax_scale, &prob);
   if (rc != INTRA_OK) return rc;
-  const int64_t blocks = int64_t(p.prob.n_tiles) * B * H;
-  if (blocks <= 0 || blocks > 0x7fffffffLL) return INTRA_ERR_UNSUPPORTED;
+  if (device < 0 || device >= MAX_DEVICES) return INTRA_ERR_BAD_ARG;
   // The launch's scratch has to fit the fixed array; a shape that needed more is turned away here.
-  if (fwd_scratch_bytes(p.prob) > NOALLOC_SCRATCH_BYTES) return INTRA_ERR_UNSUPPORTED;
+  if (fwd_scratch_bytes(prob) > NOALLOC_SCRATCH_BYTES) return INTRA_ERR_UNSUPPORTED;
 
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError());
@@ -529,22 +672,8 @@ int intra_b200_fwd_llm_noalloc(const void* q, const void* k, const void* v, void
   }
   e = cudaMemsetAsync(st.scratch, 0, sizeof(int), stream);   // the status word must start at zero
   if (e != cudaSuccess) return cuda_fail(e);
-
-  p.q = static_cast<const __nv_bfloat16*>(q);
-  p.k = static_cast<const __nv_bfloat16*>(k);
-  p.v = static_cast<const __nv_bfloat16*>(v);
-  p.o = static_cast<__nv_bfloat16*>(out);
-  p.qs = {q_strides[0], q_strides[1], q_strides[2]};
-  p.ks = {k_strides[0], k_strides[1], k_strides[2]};
-  p.vs = {v_strides[0], v_strides[1], v_strides[2]};
-  p.os = {out_strides[0], out_strides[1], out_strides[2]};
-  p.B = B; p.H = H; p.Hkv = Hkv;
-  p.scale_log2 = softmax_scale * 1.4426950408889634f;
-  p.status = st.scratch;
-  p.lse = nullptr;
-  intra_fwd_kernel<<<static_cast<unsigned>(blocks), FWD_THREADS, FWD_SMEM_BYTES, stream>>>(p);
-  e = cudaGetLastError();
-  return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
+  return launch_fwd(q, k, v, out, B, H, Hkv, q_strides, k_strides, v_strides, out_strides, prob, softmax_scale,
+                    st.scratch, st.sm_count, stream, nullptr);
 }
 
 }  // extern "C"

@@ -37,7 +37,7 @@ def _check(q, k, v):
 
     def usable(x):
         return (x.stride(-1) == 1 and x.data_ptr() % 16 == 0
-                and all(x.stride(d) % 8 == 0 for d in range(3)))
+                and all(x.stride(d) % 8 == 0 and x.stride(d) >= 0 for d in range(3)))
 
     return [x if usable(x) else x.contiguous() for x in (q, k, v)]
 
@@ -55,18 +55,27 @@ def _raise(status):
     raise ValueError(f"intra_b200: {msg}")
 
 
+def _byte_span(x):
+    """[first, last) byte addresses a tensor with non-negative strides can touch."""
+    last = sum((n - 1) * st for n, st in zip(x.shape, x.stride()) if n > 0)
+    return x.data_ptr(), x.data_ptr() + (last + 1) * x.element_size()
+
+
 def _empty_like(q, out=None, inputs=()):
     """The output tensor: the caller's `out` after checks, else a fresh tensor laid out like q."""
     if out is not None:
-        if any(out.data_ptr() == x.data_ptr() for x in inputs):
-            raise ValueError("out must not alias q, k or v: other tiles still read them while it is written")
         if out.shape != q.shape or out.dtype != q.dtype or out.device != q.device:
             raise ValueError("out must match q in shape, dtype and device")
-        if out.stride(-1) != 1 or any(out.stride(d) % 8 for d in range(3)) or out.data_ptr() % 16:
-            raise ValueError("out needs unit stride in the last dim and 16-byte aligned rows")
+        if out.stride(-1) != 1 or any(out.stride(d) % 8 or out.stride(d) <= 0 for d in range(3)) or out.data_ptr() % 16:
+            raise ValueError("out needs unit stride in the last dim, positive strides and 16-byte aligned rows")
+        lo, hi = _byte_span(out)
+        for x in inputs:
+            xlo, xhi = _byte_span(x)
+            if lo < xhi and xlo < hi:
+                raise ValueError("out must not overlap q, k or v: other tiles still read them while it is written")
         return out
     out = torch.empty_like(q)
-    if out.stride(-1) != 1 or any(out.stride(d) % 8 for d in range(3)):
+    if out.stride(-1) != 1 or any(out.stride(d) % 8 or out.stride(d) <= 0 for d in range(3)):
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     return out
 
@@ -147,7 +156,9 @@ def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *
 
 def device_status(device=None, reset=False):
     """Synchronise `device` and return the status word its kernels write when a bounded wait gives
-    up (0 = healthy). Raises nothing; callers decide."""
+    up (0 = healthy; otherwise 100 + the id of the first wait that ran out since the last reset). The
+    attention calls never poll it, and a recorded failure does not change later launches: a caller that
+    wants to know checks here, e.g. once per step. Raises nothing; callers decide."""
     import ctypes
     dev = torch.cuda.current_device() if device is None else torch.device(device).index
     word = ctypes.c_int(0)

@@ -24,27 +24,35 @@ TEXT_LEN = 512  # intra_attn/reference.py:10
 
 
 # ------------------------------------------------------------------------------------- masks
-def llm_scatter_mask(S: int, group_num: int = 8) -> np.ndarray:
+# Every builder takes an optional `rows=(r0, r1)`: only mask rows r0 <= q < r1 are built, against all S
+# keys, so that sequences whose S x S mask does not fit in memory can be checked slab by slab. The
+# predicates are the same expressions either way; tests/test_oracle.py checks slab == slice of the full
+# mask bit for bit.
+def _query_ids(S: int, rows):
+    r0, r1 = (0, S) if rows is None else rows
+    assert 0 <= r0 <= r1 <= S
+    return np.arange(r0, r1)
+
+
+def llm_scatter_mask(S: int, group_num: int = 8, rows=None) -> np.ndarray:
     """mask[q, k] = k <= q and k % G == q % G   (intra_attn/reference.py:14-17)."""
-    i = np.arange(S)
-    grp = i % group_num
-    return (grp[:, None] == grp[None, :]) & (i[None, :] <= i[:, None])
+    qi, ki = _query_ids(S, rows), np.arange(S)
+    return ((qi % group_num)[:, None] == (ki % group_num)[None, :]) & (ki[None, :] <= qi[:, None])
 
 
-def llm_gather1_mask(S: int, group_num: int = 8) -> np.ndarray:
+def llm_gather1_mask(S: int, group_num: int = 8, rows=None) -> np.ndarray:
     """Segments of G tokens, segment s in group s % G, causal  (intra_attn/reference.py:20-24)."""
-    i = np.arange(S)
-    grp = (i // group_num) % group_num
-    return (grp[:, None] == grp[None, :]) & (i[None, :] <= i[:, None])
+    qi, ki = _query_ids(S, rows), np.arange(S)
+    grp = lambda i: (i // group_num) % group_num
+    return (grp(qi)[:, None] == grp(ki)[None, :]) & (ki[None, :] <= qi[:, None])
 
 
-def llm_window_mask(S: int, window: int = 576, block: int = 64) -> np.ndarray:
+def llm_window_mask(S: int, window: int = 576, block: int = 64, rows=None) -> np.ndarray:
     """Each `block`-query block sees keys from (block start - (window - block)), clamped at 0, up
     to the query itself  (intra_attn/reference.py:27-32)."""
-    i = np.arange(S)
-    first = np.maximum((i // block) * block - (window - block), 0)
-    k = i[None, :]
-    return (k >= first[:, None]) & (k <= i[:, None])
+    qi, ki = _query_ids(S, rows), np.arange(S)
+    first = np.maximum((qi // block) * block - (window - block), 0)
+    return (ki[None, :] >= first[:, None]) & (ki[None, :] <= qi[:, None])
 
 
 def image_group_ids(width: int, text_len: int = TEXT_LEN) -> np.ndarray:
@@ -55,13 +63,14 @@ def image_group_ids(width: int, text_len: int = TEXT_LEN) -> np.ndarray:
     return np.concatenate([text, (r % 2) * 4 + (c % 4)])
 
 
-def image_scatter_mask(width: int, text_len: int = TEXT_LEN) -> np.ndarray:
+def image_scatter_mask(width: int, text_len: int = TEXT_LEN, rows=None) -> np.ndarray:
     """Every query sees all text keys plus the image keys of its own group
     (intra_attn/reference.py:49-53)."""
     g = image_group_ids(width, text_len)
     S = g.size
+    qi = _query_ids(S, rows)
     key_is_text = np.arange(S) < text_len
-    return key_is_text[None, :] | (g[:, None] == g[None, :])
+    return key_is_text[None, :] | (g[qi][:, None] == g[None, :])
 
 
 def gather0_window_start(idx: np.ndarray, n_patch: int, patch: int = 8, window: int = 16) -> np.ndarray:
@@ -71,36 +80,39 @@ def gather0_window_start(idx: np.ndarray, n_patch: int, patch: int = 8, window: 
     return np.where(idx == n_patch - 1, idx * patch - (window - patch), s)
 
 
-def image_gather0_mask(width: int, text_len: int = TEXT_LEN, patch: int = 8, window: int = 16) -> np.ndarray:
+def image_gather0_mask(width: int, text_len: int = TEXT_LEN, patch: int = 8, window: int = 16, rows=None) -> np.ndarray:
     """Image queries: all text keys + a window x window block of image keys around their patch;
     text queries keep their Scatter rows  (intra_attn/reference.py:56-74)."""
-    m = image_scatter_mask(width, text_len)
+    S = text_len + width * width
+    qi = _query_ids(S, rows)
+    m = image_scatter_mask(width, text_len, rows=rows)
     n_patch = width // patch
     r, c = np.divmod(np.arange(width * width), width)
     r0 = gather0_window_start(r // patch, n_patch, patch, window)
     c0 = gather0_window_start(c // patch, n_patch, patch, window)
-    rows_ok = (r[None, :] >= r0[:, None]) & (r[None, :] < r0[:, None] + window)
-    cols_ok = (c[None, :] >= c0[:, None]) & (c[None, :] < c0[:, None] + window)
-    m[text_len:, text_len:] = rows_ok & cols_ok
+    img = qi[qi >= text_len] - text_len                     # image queries of the slab
+    rows_ok = (r[None, :] >= r0[img][:, None]) & (r[None, :] < r0[img][:, None] + window)
+    cols_ok = (c[None, :] >= c0[img][:, None]) & (c[None, :] < c0[img][:, None] + window)
+    m[qi >= text_len, text_len:] = rows_ok & cols_ok
     return m
 
 
 def build_mask(family: str, pattern: str, S: int, group_num: int = 8, window: int = 576,
-               width: int = 64) -> np.ndarray:
+               width: int = 64, rows=None) -> np.ndarray:
     """Mask for the public API's (family, pattern) names (intra_attn/interface.py:12-13)."""
     if family == "llm":
         if pattern == "scatter":
-            return llm_scatter_mask(S, group_num)
+            return llm_scatter_mask(S, group_num, rows=rows)
         if pattern == "gather1":
-            return llm_gather1_mask(S, group_num)
+            return llm_gather1_mask(S, group_num, rows=rows)
         if pattern == "window":
-            return llm_window_mask(S, window)
+            return llm_window_mask(S, window, rows=rows)
     elif family == "image":
         assert S == TEXT_LEN + width * width
         if pattern == "scatter":
-            return image_scatter_mask(width)
+            return image_scatter_mask(width, rows=rows)
         if pattern == "gather0":
-            return image_gather0_mask(width)
+            return image_gather0_mask(width, rows=rows)
     raise KeyError((family, pattern))
 
 
@@ -150,9 +162,10 @@ def pair_count(family: str, pattern: str, S: int, group_num: int = 8, window: in
 
 
 # -------------------------------------------------------------------------------- attention
-def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask, softmax_scale=None):
-    """fp32 dense-mask attention, the reference's oracle  (intra_attn/reference.py:78-83):
-    q, k, v are (B, S, H, D) with H % H_kv == 0; mask is (S, S) bool; result in q's dtype."""
+def masked_attention_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask, softmax_scale=None):
+    """fp32 dense-mask attention as the reference's oracle computes it (intra_attn/reference.py:78-82),
+    before its final rounding to the input dtype: q, k, v are (B, S, H, D) with H % H_kv == 0; mask is
+    (S, S) bool; fp32 result (B, S, H, D)."""
     if not torch.is_tensor(mask):
         mask = torch.from_numpy(np.ascontiguousarray(mask))
     mask = mask.to(q.device)
@@ -161,29 +174,46 @@ def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask, so
     vf = v.float().permute(0, 2, 1, 3)
     out = F.scaled_dot_product_attention(qf, kf, vf, attn_mask=mask, scale=softmax_scale,
                                          enable_gqa=qf.shape[1] != kf.shape[1])
-    return out.permute(0, 2, 1, 3).to(q.dtype)
+    return out.permute(0, 2, 1, 3)
 
 
-def masked_attention_rows(q, k, v, mask, softmax_scale=None, rows: int = 1024):
-    """Same result computed with an explicit softmax over row slabs of the mask, so that long
-    sequences fit in memory and the SDPA call above has an independent cross-check."""
-    if not torch.is_tensor(mask):
-        mask = torch.from_numpy(np.ascontiguousarray(mask))
-    B, S, H, D = q.shape
+def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask, softmax_scale=None):
+    """The reference's oracle  (intra_attn/reference.py:78-83): the above, rounded to q's dtype."""
+    return masked_attention_fp32(q, k, v, mask, softmax_scale).to(q.dtype)
+
+
+def masked_attention_slab(q_rows, k, v, mask_rows, softmax_scale=None):
+    """Attention of a slab of query rows against all keys with an explicit fp32 softmax:
+    q_rows (B, R, H, D), k / v (B, S, H_kv, D), mask_rows (R, S) bool. Returns (out fp32 (B, R, H, D),
+    lse fp32 (B, H, R)). Needs no S x S mask, so it reaches sequence lengths the SDPA form cannot, and
+    it is an independent statement of the same arithmetic (tests/test_oracle.py compares the two)."""
+    if not torch.is_tensor(mask_rows):
+        mask_rows = torch.from_numpy(np.ascontiguousarray(mask_rows))
+    B, R, H, D = q_rows.shape
     Hkv = k.shape[2]
+    rep = H // Hkv
     scale = 1.0 / math.sqrt(D) if softmax_scale is None else softmax_scale
     kf = k.float().permute(0, 2, 3, 1)                       # B, Hkv, D, S
     vf = v.float().permute(0, 2, 1, 3)                       # B, Hkv, S, D
-    rep = H // Hkv
+    qs = q_rows.float().permute(0, 2, 1, 3).reshape(B, Hkv, rep, R, D)
+    s = torch.matmul(qs, kf[:, :, None]) * scale             # B, Hkv, rep, R, S
+    s = s.masked_fill(~mask_rows.to(s.device), float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse[..., None])
+    o = torch.matmul(p, vf[:, :, None])                      # B, Hkv, rep, R, D
+    return o.reshape(B, H, R, D).permute(0, 2, 1, 3), lse.reshape(B, H, R)
+
+
+def masked_attention_rows(q, k, v, mask, softmax_scale=None, rows: int = 1024):
+    """Same result as masked_attention computed slab by slab with the explicit softmax above, so that
+    long sequences fit in memory and the SDPA call has an independent cross-check."""
+    if not torch.is_tensor(mask):
+        mask = torch.from_numpy(np.ascontiguousarray(mask))
+    S = q.shape[1]
     out = torch.empty_like(q)
     for r0 in range(0, S, rows):
         r1 = min(r0 + rows, S)
-        qs = q[:, r0:r1].float().permute(0, 2, 1, 3).reshape(B, Hkv, rep, r1 - r0, D)
-        s = torch.matmul(qs, kf[:, :, None]) * scale         # B, Hkv, rep, rows, S
-        s = s.masked_fill(~mask[r0:r1].to(s.device), float("-inf"))
-        p = torch.softmax(s, dim=-1)
-        o = torch.matmul(p, vf[:, :, None])                  # B, Hkv, rep, rows, D
-        out[:, r0:r1] = o.reshape(B, H, r1 - r0, D).permute(0, 2, 1, 3).to(q.dtype)
+        out[:, r0:r1] = masked_attention_slab(q[:, r0:r1], k, v, mask[r0:r1], softmax_scale)[0].to(q.dtype)
     return out
 
 

@@ -76,20 +76,50 @@ def device_status(lib, device=0, reset=True):
     return word.value
 
 
-def oracle_attention(q, k, v, mask, scale=None, on_device=False):
+def oracle_attention(q, k, v, mask, scale=None, on_device=False, fp32=False):
     """fp32 dense-mask oracle. On the CPU by default; with on_device=True the same function runs on
-    q's device one KV-head group at a time (as the reference's kernel test does for long S)."""
+    q's device one KV-head group at a time (as the reference's kernel test does for long S). With
+    fp32=True the result is kept in fp32 instead of being rounded to q's dtype as the reference's
+    oracle does at the end."""
+    fn = oracle.masked_attention_fp32 if fp32 else oracle.masked_attention
     if not on_device:
-        return oracle.masked_attention(q.cpu(), k.cpu(), v.cpu(), mask, scale)
+        return fn(q.cpu(), k.cpu(), v.cpu(), mask, scale)
     m = torch.from_numpy(np.ascontiguousarray(mask)).to(q.device) if not torch.is_tensor(mask) else mask.to(q.device)
     H, Hkv = q.shape[2], k.shape[2]
     rep = H // Hkv
-    out = torch.empty_like(q)
+    out = torch.empty(q.shape, dtype=torch.float32 if fp32 else q.dtype, device=q.device)
     for b in range(q.shape[0]):
         for g in range(Hkv):
-            out[b:b + 1, :, g * rep:(g + 1) * rep] = oracle.masked_attention(
+            out[b:b + 1, :, g * rep:(g + 1) * rep] = fn(
                 q[b:b + 1, :, g * rep:(g + 1) * rep], k[b:b + 1, :, g:g + 1], v[b:b + 1, :, g:g + 1], m, scale)
     return out
+
+
+def bf16_ulp(x):
+    """Spacing of bfloat16 numbers around |x| (8 significant bits), elementwise, for fp32 x."""
+    mag = x.abs().clamp_min(2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(mag)) - 7)
+
+
+ULP_SLACK = 2e-3   # absolute slack beside one bf16 ulp of the reference value in check_parity
+
+
+def check_parity(out, ref32):
+    """The parity bar for a bf16 attention output against the oracle's fp32 result.
+
+    (1) The reference's stated bound: max |out - bf16(ref)| <= 1.6e-2 with the oracle rounded to bf16
+    as intra_attn/reference.py:83 does. (2) A magnitude-aware bound on top of it, against the oracle
+    before that rounding: |out - ref| <= one bf16 ulp of |ref| + 2e-3 elementwise, so that neither a
+    lucky rounding of the oracle nor a large output value decides the outcome: a half-ulp systematic
+    error on small outputs fails (2) although it passes (1). Returns the worst absolute error."""
+    assert bool(torch.isfinite(out).all()), "non-finite output"
+    o = out.float()
+    ref32 = ref32.to(o.device)
+    err1 = (o - ref32.to(torch.bfloat16).float()).abs().max().item()
+    assert err1 <= ATOL, f"max |out - bf16(oracle)| = {err1:.3e} > {ATOL}"
+    excess = ((o - ref32).abs() - (bf16_ulp(ref32) + ULP_SLACK)).max().item()
+    assert excess <= 0.0, f"an output is {excess:.3e} beyond one bf16 ulp + {ULP_SLACK} of the fp32 oracle"
+    return err1
 
 
 def max_abs_err(a, b):

@@ -32,9 +32,15 @@ def _worker(rank, world, port, result_q):
             ql, kl, vl = (x.contiguous() for x in sharded.shard_heads(q, k, v, rank, world))
             local = sharded.intra_llm_attn_sharded(ql, kl, vl, "gather1", group_num=8)
             gathered = sharded.intra_llm_attn_sharded(ql, kl, vl, "gather1", group_num=8, gather_output=True)
+            # the all-gather of one call running on its side stream under the next call
+            handle = sharded.intra_llm_attn_sharded(ql, kl, vl, "window", window=576, gather_output=True, async_gather=True)
+            again = sharded.intra_llm_attn_sharded(ql, kl, vl, "gather1", group_num=8)
+            full_w = intra_llm_attn(q, k, v, "window", window=576)
+            gathered_w = handle.wait()
         qs, _ = sharded.head_slices(32, 8, rank, world)
         torch.cuda.synchronize()
-        result_q.put((rank, bool(torch.equal(local, full[:, :, qs])), bool(torch.equal(gathered, full))))
+        result_q.put((rank, bool(torch.equal(local, full[:, :, qs])) and bool(torch.equal(again, local)),
+                      bool(torch.equal(gathered, full)) and bool(torch.equal(gathered_w, full_w))))
     finally:
         dist.destroy_process_group()
 

@@ -67,3 +67,29 @@ def test_masked_lse_matches_direct_logsumexp_and_softmax():
     out = torch.einsum("bhqk,bkhd->bqhd", p, v.float().repeat_interleave(2, dim=2))
     ref = oracle.masked_attention(q, k, v, mask).float()
     assert float((out - ref).abs().max()) <= 1e-2
+
+
+@pytest.mark.parametrize("case", [c for c in MASK_CASES if c["S"] <= 4608], ids=_util.case_id)
+def test_mask_row_slabs_equal_slices_of_the_full_mask(case):
+    """The row-slab form of every mask builder (what the parity tests at S = 32768 and 65536 use, where
+    the S x S mask cannot be built) is bit for bit the corresponding slice of the pinned full mask."""
+    S, kw = case["S"], _util.case_kwargs(case)
+    full = oracle.build_mask(case["family"], case["pattern"], S, **kw)
+    for r0, r1 in ((0, min(S, 100)), (S // 3, min(S, S // 3 + 517)), (max(S - 129, 0), S), (500, min(S, 700))):
+        if r0 >= r1:
+            continue
+        assert np.array_equal(oracle.build_mask(case["family"], case["pattern"], S, rows=(r0, r1), **kw), full[r0:r1])
+
+
+def test_slab_attention_matches_sdpa_form():
+    """masked_attention_slab (explicit softmax, one slab of query rows) against the SDPA form that is
+    pinned to the reference's outputs, including its log-sum-exp against masked_lse."""
+    q, k, v = oracle.make_inputs(2, 700, 4, 2, seed=3)
+    for mask in (oracle.llm_window_mask(700, 200), oracle.llm_gather1_mask(700, 4)):
+        ref = oracle.masked_attention_fp32(q, k, v, mask)
+        lse_ref = oracle.masked_lse(q, k, torch.from_numpy(mask))
+        for r0, r1 in ((0, 128), (300, 700)):
+            out, lse = oracle.masked_attention_slab(q[:, r0:r1], k, v, mask[r0:r1])
+            assert out.dtype == torch.float32 and out.shape == (2, r1 - r0, 4, 128)
+            assert float((out - ref[:, r0:r1]).abs().max()) <= 2e-5
+            assert float((lse - lse_ref[:, :, r0:r1]).abs().max()) <= 2e-5

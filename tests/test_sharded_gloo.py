@@ -47,6 +47,22 @@ def _worker(rank, world, port, mode, result_q):
             ref = oracle.masked_attention(q, k, v, mask)
             qs, _ = sharded.head_slices(H, Hkv, rank, world)
             result_q.put((rank, bool(torch.equal(out, ref[:, :, qs]))))
+        elif mode == "async":
+            handle = sharded.sharded_attn(_oracle_local(mask), ql, kl, vl, gather_output=True, async_gather=True)
+            ref = oracle.masked_attention(q, k, v, mask)
+            result_q.put((rank, bool(torch.equal(handle.wait(), ref))))
+        elif mode == "fail-local":
+            # without a collective to protect there is no agreement: the failing rank raises its own
+            # error, the healthy one returns its block, nobody waits for anybody
+            def bad_local(qq, kk, vv, *a, **kw):
+                if rank == 1:
+                    raise RuntimeError("injected launch failure")
+                return oracle.masked_attention(qq, kk, vv, mask)
+            try:
+                out = sharded.sharded_attn(bad_local, ql, kl, vl, gather_output=False)
+                result_q.put((rank, rank == 0 and out.shape[2] == H // world))
+            except RuntimeError as e:
+                result_q.put((rank, rank == 1 and "injected" in str(e)))
         elif mode == "fail":
             def bad(qq, kk, vv, *a, **kw):
                 if rank == 1:
@@ -61,7 +77,7 @@ def _worker(rank, world, port, mode, result_q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["gather", "local", "fail"])
+@pytest.mark.parametrize("mode", ["gather", "local", "async", "fail", "fail-local"])
 def test_sharded_world2(mode):
     world = 2
     ctx = mp.get_context("spawn")
