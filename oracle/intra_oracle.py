@@ -24,14 +24,21 @@ TEXT_LEN = 512  # intra_attn/reference.py:10
 
 
 # ------------------------------------------------------------------------------------- masks
-# Every builder takes an optional `rows=(r0, r1)`: only mask rows r0 <= q < r1 are built, against all S
-# keys, so that sequences whose S x S mask does not fit in memory can be checked slab by slab. The
+# Every builder takes an optional `rows` ((r0, r1) or an array of query ids): only those mask rows are
+# built, against all S keys, so that sequences whose S x S mask does not fit in memory can be checked slab by slab. The
 # predicates are the same expressions either way; tests/test_oracle.py checks slab == slice of the full
 # mask bit for bit.
 def _query_ids(S: int, rows):
-    r0, r1 = (0, S) if rows is None else rows
-    assert 0 <= r0 <= r1 <= S
-    return np.arange(r0, r1)
+    """Query token ids of the mask rows to build: all, a (r0, r1) range, or an explicit index array."""
+    if rows is None:
+        return np.arange(S)
+    if isinstance(rows, tuple):
+        r0, r1 = rows
+        assert 0 <= r0 <= r1 <= S
+        return np.arange(r0, r1)
+    qi = np.asarray(rows, dtype=np.int64)
+    assert qi.ndim == 1 and (qi.size == 0 or (qi.min() >= 0 and qi.max() < S))
+    return qi
 
 
 def llm_scatter_mask(S: int, group_num: int = 8, rows=None) -> np.ndarray:

@@ -79,6 +79,8 @@ def test_mask_row_slabs_equal_slices_of_the_full_mask(case):
         if r0 >= r1:
             continue
         assert np.array_equal(oracle.build_mask(case["family"], case["pattern"], S, rows=(r0, r1), **kw), full[r0:r1])
+    picked = np.arange(3, S, 37)
+    assert np.array_equal(oracle.build_mask(case["family"], case["pattern"], S, rows=picked, **kw), full[picked])
 
 
 def test_slab_attention_matches_sdpa_form():
