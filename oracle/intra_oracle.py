@@ -189,11 +189,13 @@ def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask, so
     return masked_attention_fp32(q, k, v, mask, softmax_scale).to(q.dtype)
 
 
-def masked_attention_slab(q_rows, k, v, mask_rows, softmax_scale=None):
+def masked_attention_slab(q_rows, k, v, mask_rows, softmax_scale=None, with_spread=False):
     """Attention of a slab of query rows against all keys with an explicit fp32 softmax:
     q_rows (B, R, H, D), k / v (B, S, H_kv, D), mask_rows (R, S) bool. Returns (out fp32 (B, R, H, D),
     lse fp32 (B, H, R)). Needs no S x S mask, so it reaches sequence lengths the SDPA form cannot, and
-    it is an independent statement of the same arithmetic (tests/test_oracle.py compares the two)."""
+    it is an independent statement of the same arithmetic (tests/test_oracle.py compares the two).
+    with_spread=True appends sum_j p_j |v_j| (fp32, shaped like out): the scale of the terms that were
+    added up, against which a rounding error of the probabilities has to be judged."""
     if not torch.is_tensor(mask_rows):
         mask_rows = torch.from_numpy(np.ascontiguousarray(mask_rows))
     B, R, H, D = q_rows.shape
@@ -207,8 +209,11 @@ def masked_attention_slab(q_rows, k, v, mask_rows, softmax_scale=None):
     s = s.masked_fill(~mask_rows.to(s.device), float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse[..., None])
-    o = torch.matmul(p, vf[:, :, None])                      # B, Hkv, rep, R, D
-    return o.reshape(B, H, R, D).permute(0, 2, 1, 3), lse.reshape(B, H, R)
+    shape = lambda o: o.reshape(B, H, R, D).permute(0, 2, 1, 3)
+    out = shape(torch.matmul(p, vf[:, :, None]))             # B, R, H, D
+    if with_spread:
+        return out, lse.reshape(B, H, R), shape(torch.matmul(p, vf.abs()[:, :, None]))
+    return out, lse.reshape(B, H, R)
 
 
 def masked_attention_rows(q, k, v, mask, softmax_scale=None, rows: int = 1024):

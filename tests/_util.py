@@ -101,25 +101,45 @@ def bf16_ulp(x):
     return torch.exp2(torch.floor(torch.log2(mag)) - 7)
 
 
-ULP_SLACK = 2e-3   # absolute slack beside one bf16 ulp of the reference value in check_parity
+BIAS_MAX = 2e-6    # |mean signed error|: measured <= 1.4e-7 on the reference's test matrix
+RMS_MAX = 1e-3     # root-mean-square error: measured 1.1e-4 .. 3.3e-4
 
 
-def check_parity(out, ref32):
+def check_parity(out, ref32, spread):
     """The parity bar for a bf16 attention output against the oracle's fp32 result.
 
     (1) The reference's stated bound: max |out - bf16(ref)| <= 1.6e-2 with the oracle rounded to bf16
-    as intra_attn/reference.py:83 does. (2) A magnitude-aware bound on top of it, against the oracle
-    before that rounding: |out - ref| <= one bf16 ulp of |ref| + 2e-3 elementwise, so that neither a
-    lucky rounding of the oracle nor a large output value decides the outcome: a half-ulp systematic
-    error on small outputs fails (2) although it passes (1). Returns the worst absolute error."""
+    as intra_attn/reference.py:83 does.
+    (2) A magnitude-aware bound on top of it, against the oracle BEFORE that rounding, so that neither a
+    lucky rounding of the oracle nor a large output value decides the outcome:
+        |out - ref| <= one bf16 ulp of |ref|  +  2^-8 * spread,     spread = sum_j p_j |v_j|.
+    The first term is the output's own rounding (half an ulp) with a factor two of margin. The second
+    covers what the reference's kernels do as well (flash_fwd_kernel.h:5607): the probabilities are
+    rounded to bf16 (relative error <= 2^-9 each) before they multiply V, which perturbs the result by
+    at most 2^-9 * spread - a quantity that does not shrink when the terms cancel, which is why a bound
+    in ulps of |ref| alone cannot hold; again a factor two of margin.
+    (3) No systematic error: |mean(out - ref)| <= 2e-6 and rms(out - ref) <= 1e-3. A half-ulp bias on
+    outputs of typical size (2.5e-4 and more) would pass (1) and (2) and fails here.
+    Returns the worst absolute error of (1)."""
     assert bool(torch.isfinite(out).all()), "non-finite output"
     o = out.float()
-    ref32 = ref32.to(o.device)
+    ref32, spread = ref32.to(o.device), spread.to(o.device)
     err1 = (o - ref32.to(torch.bfloat16).float()).abs().max().item()
     assert err1 <= ATOL, f"max |out - bf16(oracle)| = {err1:.3e} > {ATOL}"
-    excess = ((o - ref32).abs() - (bf16_ulp(ref32) + ULP_SLACK)).max().item()
-    assert excess <= 0.0, f"an output is {excess:.3e} beyond one bf16 ulp + {ULP_SLACK} of the fp32 oracle"
+    d = o - ref32
+    excess = (d.abs() - (bf16_ulp(ref32) + spread / 256)).max().item()
+    assert excess <= 0.0, f"an output is {excess:.3e} beyond one bf16 ulp + 2^-8 of the summed terms"
+    bias, rms = d.mean().item(), d.pow(2).mean().sqrt().item()
+    bias_max = max(BIAS_MAX, 6 * rms / d.numel() ** 0.5)      # small tensors: six standard errors of the mean
+    assert abs(bias) <= bias_max and rms <= RMS_MAX, f"systematic error: mean {bias:.3e}, rms {rms:.3e}"
     return err1
+
+
+def check_against_oracle(out, q, k, v, mask, scale=None):
+    """check_parity with the oracle run on q's device: fp32 result and the spread of its terms."""
+    ref = oracle_attention(q, k, v, mask, scale, on_device=True, fp32=True)
+    spread = oracle_attention(q, k, v.abs(), mask, scale, on_device=True, fp32=True)
+    return check_parity(out, ref, spread)
 
 
 def max_abs_err(a, b):

@@ -100,7 +100,7 @@ def test_llm_matrix(lib, pattern, S, B, H, Hkv, param):
     assert rc == 0
     kw = {"window": param} if pattern == "window" else {"group_num": param}
     mask = oracle.build_mask("llm", pattern, S, **kw)
-    _util.check_parity(out, _util.oracle_attention(q, k, v, mask, on_device=True, fp32=True))
+    _util.check_against_oracle(out, q, k, v, mask)
 
 
 @pytest.mark.parametrize("width,H", [(64, 24), (128, 8)])
@@ -113,7 +113,7 @@ def test_image_matrix(lib, pattern, B, width, H):
     rc, out = _util.call_fwd(lib, "image", pattern, q, k, v, width)
     assert rc == 0
     mask = oracle.build_mask("image", pattern, S, width=width)
-    _util.check_parity(out, _util.oracle_attention(q, k, v, mask, on_device=True, fp32=True))
+    _util.check_against_oracle(out, q, k, v, mask)
 
 
 # The five BASELINE configurations at their full sizes. Their S x S masks do not fit anywhere, so the
@@ -148,14 +148,18 @@ def test_baseline_configs_full_size(lib, name, family, pattern, S, H, Hkv, kw, g
     starts = sorted({0, S // 2 - SLAB // 2, S - SLAB, min(128 * 37 + 71, S - SLAB)})
     worst = 0.0
     checked = 0
-    for r0 in range(0, S, SLAB) if group_rows else starts:
+    first_groups = 1 if family == "llm" else 3
+    plan = [(r0, range(Hkv)) for r0 in starts]
+    if group_rows:
+        plan += [(r0, range(first_groups)) for r0 in range(0, S, SLAB)]
+    for r0, groups in plan:
         r1 = min(r0 + SLAB, S)
         mask_rows = torch.from_numpy(oracle.build_mask(family, pattern, S, rows=(r0, r1), **kw)).cuda()
-        all_heads = r0 in starts
-        for g in range(Hkv if all_heads else (1 if family == "llm" else 3)):
+        for g in groups:
             hs = slice(g * rep, (g + 1) * rep)
-            ref, ref_lse = oracle.masked_attention_slab(q[:, r0:r1, hs], k[:, :, g:g + 1], v[:, :, g:g + 1], mask_rows)
-            worst = max(worst, _util.check_parity(out[:, r0:r1, hs], ref))
+            ref, ref_lse, spread = oracle.masked_attention_slab(q[:, r0:r1, hs], k[:, :, g:g + 1], v[:, :, g:g + 1],
+                                                                mask_rows, with_spread=True)
+            worst = max(worst, _util.check_parity(out[:, r0:r1, hs], ref, spread))
             assert float((lse[:, hs, r0:r1] - ref_lse).abs().max()) <= LSE_ATOL
             checked += (r1 - r0) * rep
     assert checked >= 4 * SLAB * H
@@ -254,7 +258,7 @@ def test_bounded_wait_gives_up_and_reports(lib):
     q, k, v = oracle.make_inputs(1, 512, 2, 2, seed=43, device="cuda")      # the device still works
     rc, out = _util.call_fwd(lib, "llm", "window", q, k, v, 576)
     assert rc == 0
-    _util.check_parity(out, _util.oracle_attention(q, k, v, oracle.llm_window_mask(512, 576), on_device=True, fp32=True))
+    _util.check_against_oracle(out, q, k, v, oracle.llm_window_mask(512, 576))
 
 
 @pytest.mark.parametrize("family,pattern,S,param", [
@@ -478,7 +482,7 @@ def test_forced_kernel_paths(lib, _launcher_choice_restored, no_tma, split):
             fn = intra_image_attn if family == "image" else intra_llm_attn
             out, lse = fn(q, k, v, pattern, strict=False, return_lse=True, **kw)
             mask = torch.from_numpy(oracle.build_mask(family, pattern, S, **kw)).cuda()
-            _util.check_parity(out, oracle.masked_attention_fp32(q, k, v, mask))
+            _util.check_parity(out, oracle.masked_attention_fp32(q, k, v, mask), oracle.masked_attention_fp32(q, k, v.abs(), mask))
             assert float((lse - oracle.masked_lse(q, k, mask)).abs().max()) <= LSE_ATOL, (family, pattern)
 
 

@@ -38,8 +38,9 @@ with torch.no_grad():
         else:
             ours, theirs = intra_image_attn(q, k, v, pattern, **kw), ref.image(q, k, v, pattern, **kw)
         torch.cuda.synchronize()
-        want = _util.oracle_attention(q, k, v, oracle.build_mask(family, pattern, S, **kw), on_device=True, fp32=True)
-        e_ours = _util.check_parity(ours, want)
+        mask = oracle.build_mask(family, pattern, S, **kw)
+        want = _util.oracle_attention(q, k, v, mask, on_device=True, fp32=True)
+        e_ours = _util.check_against_oracle(ours, q, k, v, mask)
         e_ref = (theirs.float() - want.to(torch.bfloat16).float()).abs().max().item()
         diff = (ours.float() - theirs.float()).abs().max().item()
         print(f"PARITY {family}/{pattern} S={S}: ours {e_ours:.3e}  reference kernel {e_ref:.3e}  ours-vs-reference {diff:.3e}")
