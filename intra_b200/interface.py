@@ -80,6 +80,36 @@ def _empty_like(q, out=None, inputs=()):
     return out
 
 
+# Validated call plans, keyed by everything the checks above look at (addresses, shapes, strides,
+# dtypes, device, requires_grad). A serving loop or a layer stack calls with the same tensors over and
+# over; at S = 4096 a call is 40 us of GPU time and the checks would cost as much on the host again.
+_PLANS = {}
+_PLANS_MAX = 512
+
+
+def _plan(q, k, v, out):
+    """(q, k, v, out or None, B, S, H, Hkv, q/k/v/out stride arrays or None for out) after the checks."""
+    rg = q.requires_grad or k.requires_grad or v.requires_grad
+    if rg and torch.is_grad_enabled():
+        raise RuntimeError("INTRA kernels are forward-only; call them under torch.no_grad()")
+    key = (q.data_ptr(), k.data_ptr(), v.data_ptr(), None if out is None else (out.data_ptr(), out.shape, out.stride(), out.dtype, out.device),
+           q.shape, k.shape, v.shape, q.stride(), k.stride(), v.stride(), q.dtype, k.dtype, v.dtype, q.device, k.device, v.device)
+    plan = _PLANS.get(key)
+    if plan is not None:
+        return (q, k, v) + plan
+    q2, k2, v2 = _check(q, k, v)
+    copied = q2 is not q or k2 is not k or v2 is not v        # fresh contiguous copies: nothing to remember
+    if out is not None:
+        _empty_like(q2, out, (q2, k2, v2))
+    B, S, H, _ = q2.shape
+    plan = (B, S, H, k2.shape[2], strides3(q2), strides3(k2), strides3(v2), None if out is None else strides3(out))
+    if not copied:
+        if len(_PLANS) >= _PLANS_MAX:
+            _PLANS.clear()
+        _PLANS[key] = plan
+    return (q2, k2, v2) + plan
+
+
 def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_scale=None, *, strict=True,
                    return_lse=False, out=None):
     """Causal prefill attention for language models.
@@ -96,21 +126,22 @@ def intra_llm_attn(q, k, v, pattern="scatter", group_num=8, window=576, softmax_
     denominator, which is what merging attention over disjoint key sets needs. `out=` (not in the
     reference, which always allocates) writes into a tensor of the caller's; it must not alias q, k, v.
     """
-    q, k, v = _check(q, k, v)
-    if strict and pattern == "gather1" and (group_num != 8 or q.shape[1] % (group_num * group_num)):
-        raise ValueError(f"gather1 needs group_num=8 and seqlen % 64 == 0, got G={group_num}, S={q.shape[1]}")
+    q, k, v, B, S, H, Hkv, qs, ks, vs, os_ = _plan(q, k, v, out)
+    if strict and pattern == "gather1" and (group_num != 8 or S % (group_num * group_num)):
+        raise ValueError(f"gather1 needs group_num=8 and seqlen % 64 == 0, got G={group_num}, S={S}")
     pid = LLM_PATTERNS[pattern]
-    out = _empty_like(q, out, (q, k, v))
-    B, S, H, _ = q.shape
-    tail = (strides3(q), strides3(k), strides3(v), strides3(out), pid, int(group_num), int(window),
-            _scale(q, softmax_scale), q.device.index, torch.cuda.current_stream(q.device).cuda_stream)
+    if out is None:
+        out = _empty_like(q)
+        os_ = strides3(out)
+    dev = q.device
+    tail = (qs, ks, vs, os_, pid, int(group_num), int(window), _scale(q, softmax_scale), dev.index,
+            torch.cuda.current_stream(dev).cuda_stream)
     if return_lse:
-        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=dev)
         rc = lib.intra_b200_fwd_llm_lse(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                        B, S, H, k.shape[2], *tail)
+                                        B, S, H, Hkv, *tail)
     else:
-        rc = lib.intra_b200_fwd_llm(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H, k.shape[2],
-                                    *tail)
+        rc = lib.intra_b200_fwd_llm(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, S, H, Hkv, *tail)
     if rc != 0:
         _raise(rc)
     return (out, lse) if return_lse else out
@@ -129,22 +160,24 @@ def intra_image_attn(q, k, v, pattern="scatter", width=64, softmax_scale=None, *
     the reference) accepts any width that is a multiple of 8 and at least 16. `return_lse=True` returns
     `(out, lse)` and `out=` writes into the caller's tensor, as in intra_llm_attn.
     """
-    q, k, v = _check(q, k, v)
+    q, k, v, B, S, H, Hkv, qs, ks, vs, os_ = _plan(q, k, v, out)
     if not strict and (width < 16 or width % 8):
         raise ValueError("width must be a multiple of 8 and at least 16")
     if strict and width not in (64, 128):
         raise ValueError("image kernels are compiled for width 64 and 128")
-    if q.shape[1] != TEXT_LEN + width * width:
-        raise ValueError(f"expected {TEXT_LEN} text + {width}x{width} image tokens, got {q.shape[1]}")
-    if k.shape[2] != q.shape[2]:
+    if S != TEXT_LEN + width * width:
+        raise ValueError(f"expected {TEXT_LEN} text + {width}x{width} image tokens, got {S}")
+    if Hkv != H:
         raise ValueError("image attention is multi-head: k/v need as many heads as q")
     pid = IMAGE_PATTERNS[pattern]
-    out = _empty_like(q, out, (q, k, v))
-    B, S, H, _ = q.shape
-    tail = (strides3(q), strides3(k), strides3(v), strides3(out), pid, int(width), _scale(q, softmax_scale),
-            q.device.index, torch.cuda.current_stream(q.device).cuda_stream)
+    if out is None:
+        out = _empty_like(q)
+        os_ = strides3(out)
+    dev = q.device
+    tail = (qs, ks, vs, os_, pid, int(width), _scale(q, softmax_scale), dev.index,
+            torch.cuda.current_stream(dev).cuda_stream)
     if return_lse:
-        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=dev)
         rc = lib.intra_b200_fwd_image_lse(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                                           B, S, H, *tail)
     else:
