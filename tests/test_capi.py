@@ -81,3 +81,24 @@ def test_no_cpu_fallback(lib):
                                 0, 8, 576, 0.088, 0, None)
     assert rc in (-4, -5)
     assert bool((out == 7.0).all())
+
+
+def test_helper_entry_points_reject_bad_arguments(lib):
+    """The head-interleave entry point and the test hooks check their arguments before touching a GPU."""
+    buf = torch.zeros(1024, dtype=torch.uint8)
+    p = buf.data_ptr()
+    assert p % 16 == 0
+    f = lib.intra_b200_interleave_heads
+    assert f(None, p, 2, 4, 256, 0, None) == -1
+    assert f(p, p, 0, 4, 256, 0, None) == -1
+    assert f(p, p, 2, 0, 256, 0, None) == -1
+    assert f(p, p, 2, 4, 8, 0, None) == -3                  # blocks must be multiples of 16 bytes
+    assert f(p + 4, p, 2, 4, 256, 0, None) == -3
+    assert lib.intra_b200_test_force_path(0, 3) == -1
+    assert lib.intra_b200_test_force_path(0, 0) == 0
+    assert lib.intra_b200_test_wait_timeout(0, p, 0, None) == -1       # limit out of range
+    assert lib.intra_b200_test_wait_timeout(5000, p, 0, None) == -1
+    assert lib.intra_b200_test_wait_timeout(5, None, 0, None) == -1
+    n = ctypes.c_int64(0)
+    assert lib.intra_b200_test_tma_rows(p, p, p, 1, 256, 2, 1, None, None, None, 0, 0, 8, None, None, None, None, None,
+                                        ctypes.byref(n), ctypes.byref(n), 0, None) == -1   # no strides

@@ -224,6 +224,18 @@ def test_tma_tiles_hold_the_rows_the_index_maps_name(lib, case, heads):
         assert bad.size == 0, f"{what} rows differ at {bad[:8]}: got {got[bad[:8]]}, want {want[bad[:8]]}"
 
 
+@pytest.mark.parametrize("world,B,S,Hl", [(2, 1, 4096, 16), (8, 2, 1000, 4), (3, 1, 77, 1)])
+def test_interleave_heads_kernel(lib, world, B, S, Hl):
+    """The multi-GPU launcher's reorder kernel on one GPU: rank-major blocks of an all-gather into
+    (batch, token, head, 128) order, bit for bit against a torch permute."""
+    from intra_b200 import sharded
+    parts = torch.randn(world, B, S, Hl, 128, device="cuda").to(torch.bfloat16)
+    got = sharded.interleave_heads(parts)
+    want = parts.permute(1, 2, 0, 3, 4).reshape(B, S, world * Hl, 128)
+    torch.cuda.synchronize()
+    assert got.shape == want.shape and torch.equal(got, want)
+
+
 def test_status_word_is_sticky_but_launches_go_on(lib):
     """The documented behaviour of the status word: a recorded failure stays until it is reset and is
     reported by intra_b200_device_status, and launches made meanwhile still compute their outputs. The
