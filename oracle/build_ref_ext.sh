@@ -10,7 +10,7 @@
 # not run.  Its un-vendored CUTLASS submodule (csrc/cutlass, empty in the checkout) is replaced
 # by the CUTLASS/CuTe header tree that ships inside the flashinfer wheel of this image.
 #
-# usage: oracle/build_ref_ext.sh [REFERENCE_DIR]      (default /root/reference)
+# usage: oracle/build_ref_ext.sh [REFERENCE_DIR]      (default: where the build container keeps the reference checkout)
 set -euo pipefail
 REF="${1:-/root/reference}"
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
