@@ -401,7 +401,29 @@ def run_ours(args):
                     b_.record(stream)
                 torch.cuda.synchronize()
                 extra_calls.append((c, S2, call_flops(c[0], c[1], c[2], S2, H2),
-                                    statistics.mean(a_.elapsed_time(b_) for a_, b_ in pairs)))
+                                    statistics.mean(a_.elapsed_time(b_) for a_, b_ in pairs), "intra_llm_attn"))
+            # the Gather-1 call once more through the allocation-free C entry point (same kernel, scratch in
+            # the library image), so that this entry point has a measured line of its own
+            import ctypes
+
+            from intra_b200._loader import lib as _lib, strides3 as _st
+            c = calls2[0]
+            args2 = (q2.data_ptr(), k2.data_ptr(), v2.data_ptr(), o2.data_ptr(), B2, S2, H2, Hkv2, _st(q2), _st(k2), _st(v2),
+                     _st(o2), 1, c[2]["group_num"], 576, HEAD_DIM ** -0.5, local_rank, stream.cuda_stream, None)
+            for _ in range(5):
+                assert _lib.intra_b200_fwd_llm_noalloc(*args2) == 0
+            torch.cuda.synchronize()
+            time.sleep(0.5)
+            pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n2)]
+            for a_, b_ in pairs:
+                a_.record(stream)
+                _lib.intra_b200_fwd_llm_noalloc(*args2)
+                b_.record(stream)
+            torch.cuda.synchronize()
+            prev = ctypes.c_int(-1)
+            assert _lib.intra_b200_fwd_llm_noalloc(*args2[:-1], ctypes.byref(prev)) == 0 and prev.value == 0
+            extra_calls.append((c, S2, call_flops(c[0], c[1], c[2], S2, H2),
+                                statistics.mean(a_.elapsed_time(b_) for a_, b_ in pairs), "intra_b200_fwd_llm_noalloc (C ABI)"))
             del q2, k2, v2, o2
 
         # ---- end-to-end: pinned host buffers in, host buffers out, every step. Three streams pipeline
@@ -475,14 +497,15 @@ def run_ours(args):
         peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
         sustained = float(peaks.get("bf16_tflops_sustained", peak))
 
-        def call_entry(c, S_, flops, ms, per):
+        def call_entry(c, S_, flops, ms, per, entry="intra_b200.sharded"):
             tf = flops / ms / 1e9
-            return {"pattern": f"{c[0]}/{c[1]}", **c[2], "S": S_, "heads": per, "ms": ms, "tflops": tf,
+            return {"pattern": f"{c[0]}/{c[1]}", **c[2], "S": S_, "heads": per, "entry": entry, "ms": ms, "tflops": tf,
                     "frac_of_burst_peak": tf / peak, "frac_of_sustained_peak": tf / sustained}
 
         per_heads = f"{H}q/{Hkv}kv per GPU"
         call_list = [call_entry(c, S, flops_calls[i], launch_ms[i], per_heads) for i, c in enumerate(calls)]
-        call_list += [call_entry(c, S2, fl, ms, "32q/8kv, 20 launches back to back after a 0.5 s pause, outside the timed region") for c, S2, fl, ms in extra_calls]
+        call_list += [call_entry(c, S2, fl, ms, "32q/8kv, 20 launches back to back after a 0.5 s pause, outside the timed region", ent)
+                      for c, S2, fl, ms, ent in extra_calls]
         line = {
             "metric": "effective sparse attention throughput (4*d*H*attended pairs / time)",
             "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
