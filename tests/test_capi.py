@@ -58,6 +58,11 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     assert call(args(q=ptr + 2)) == -3
     bad = (ctypes.c_int64 * 3)(q.stride(0), q.stride(1) + 4, q.stride(2))
     assert lib.intra_b200_fwd_llm(ptr, ptr, ptr, ptr, 1, 256, 2, 1, bad, s, s, s, 0, 8, 576, 0.088, 0, None) == -3
+    # an output whose heads (or tokens) share memory: different tiles would write the same rows
+    expanded = (ctypes.c_int64 * 3)(q.stride(0), q.stride(1), 0)
+    assert lib.intra_b200_fwd_llm(ptr, ptr, ptr, ptr, 1, 256, 2, 1, s, s, s, expanded, 0, 8, 576, 0.088, 0, None) == -1
+    negative = (ctypes.c_int64 * 3)(q.stride(0), -q.stride(1), q.stride(2))
+    assert lib.intra_b200_fwd_llm(ptr, ptr, ptr, ptr, 1, 256, 2, 1, s, s, s, negative, 0, 8, 576, 0.088, 0, None) == -1
     assert lib.intra_b200_fwd_image(ptr, ptr, ptr, ptr, 1, 256, 2, s, s, s, s, 0, 64, 0.088, 0, None) == -2
     assert lib.intra_b200_fwd_image(ptr, ptr, ptr, ptr, 1, 512 + 4096, 2, s, s, s, s, 1, 64, 0.088, 0, None) == -2
 
