@@ -55,25 +55,10 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
 // Wait for the phase with the given parity to complete. Gives up (returns false) when another
 // thread of the CTA has raised *abort_flag or after `limit_ms` without progress, so that a protocol
 // error ends as a reported status instead of a hung kernel.
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           uint32_t limit_ms = 2000) {
-#ifdef INTRA_SPIN_WAIT
-#pragma unroll 1
-  for (int i = 0; i < INTRA_SPIN_WAIT; ++i)
-    if (mbar_test_wait(bar, parity)) return true;
-#else
   if (mbar_try_wait(bar, parity)) return true;
   if (mbar_try_wait(bar, parity)) return true;
-#endif
   return mbar_wait_slow(smem_u32(bar), parity, abort_flag, limit_ms);
 }
 __device__ __forceinline__ void fence_mbar_init() {
