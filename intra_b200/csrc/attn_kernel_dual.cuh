@@ -39,20 +39,27 @@ namespace intra {
 // warpgroup), 128 / NSPLIT score columns each. Two instantiations: NSPLIT = 4 (768 threads) hides more
 // latency and wins on short items, NSPLIT = 2 (512 threads) leaves the MMA-issuing warp's scheduler
 // less crowded and wins on long ones; the host picks by the key tiles per item.
+//
+// NSPLIT = 1 is a different pipeline for long items (the "row-owner" form): the softmax warps form two
+// sets of four, one per sub-tile, a thread owning its query row alone (no exchange of maxima). Both
+// sub-tiles' QK^T go to ONE score buffer in tensor memory, which a set copies to registers and hands
+// back at once, while P has a buffer of its own per sub-tile. The tensor core then never waits for a
+// softmax phase, only for the copy, and a set has a whole key-tile period for its phase while the
+// other set's phase runs beside it and fills its latencies.
 template <int NSPLIT>
 struct DualCfg {
-  static_assert(NSPLIT == 2 || NSPLIT == 4, "softmax column split must be 2 or 4");
+  static_assert(NSPLIT == 1 || NSPLIT == 2 || NSPLIT == 4, "softmax column split must be 1 (row-owner form), 2 or 4");
   static constexpr int COLS = TILE_N / NSPLIT;            // score columns per softmax thread
-  static constexpr int SM_WARPS = 4 * NSPLIT;             // softmax warps
-  static constexpr int SM_THREADS = 128 * NSPLIT;
+  static constexpr int SM_WARPS = NSPLIT == 1 ? 8 : 4 * NSPLIT;   // softmax warps
+  static constexpr int SM_THREADS = 32 * SM_WARPS;
   static constexpr int THREADS = SM_THREADS + 256;        // + epilogue / loader warpgroup + MMA / TMA warpgroup
   // setmaxnreg budgets: softmax, epilogue / loaders, MMA / TMA / planner. The last group must not spill:
   // a local-memory access in the MMA-issuing thread's loop stalls the tensor pipe. Sums: 512 threads
   // start with 128 registers each (65536), 768 threads with 80 (61440).
-  static constexpr int SM_REGS = NSPLIT == 2 ? 176 : 88;
-  static constexpr int EP_REGS = 64;
-  static constexpr int MMA_REGS = NSPLIT == 2 ? 96 : 64;
-  static_assert(SM_THREADS * SM_REGS + 128 * (EP_REGS + MMA_REGS) <= (NSPLIT == 2 ? 65536 : 61440),
+  static constexpr int SM_REGS = NSPLIT == 1 ? 184 : NSPLIT == 2 ? 176 : 88;
+  static constexpr int EP_REGS = NSPLIT == 1 ? 48 : 64;
+  static constexpr int MMA_REGS = NSPLIT == 1 ? 96 : NSPLIT == 2 ? 96 : 64;
+  static_assert(SM_THREADS * SM_REGS + 128 * (EP_REGS + MMA_REGS) <= (NSPLIT == 4 ? 61440 : 65536),
                 "register budgets exceed what the CTA was launched with: setmaxnreg.inc would never return");
 };
 constexpr int KV_STAGES = 2;
@@ -441,7 +448,10 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
   //           14 l_ready (row sums of an item published), 15-16 o_free[s] (O of an item has been read),
   //           17 q1_full (barrier 0 is Q0's)
   //           18-21 slot_ready[r], 22-25 slot_free[r] (item ring)
-  __shared__ uint64_t bars[18 + 2 * ITEM_RING];
+  //           row-owner form only: 26-27 s_taken[s] (the set has copied its scores out of the shared buffer),
+  //           28 pv0_done (a PV of sub-tile 0 has completed), 29-30 v_done[key tile & 1] (PV1 of that key tile
+  //           and everything its warp issued before), 31 l_ready of sub-tile 1, 32 the PV warp's drain
+  __shared__ uint64_t bars[18 + 2 * ITEM_RING + 7];
   __shared__ ItemSlot ring[ITEM_RING];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
@@ -467,6 +477,11 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
   uint64_t* o_free = &bars[15];
   uint64_t* slot_ready = &bars[18];
   uint64_t* slot_free = &bars[18 + ITEM_RING];
+  uint64_t* s_taken = &bars[18 + 2 * ITEM_RING];
+  uint64_t* pv0_done = &bars[18 + 2 * ITEM_RING + 2];
+  uint64_t* v_done = &bars[18 + 2 * ITEM_RING + 3];
+  uint64_t* l_ready1 = &bars[18 + 2 * ITEM_RING + 5];
+  uint64_t* drain2 = &bars[18 + 2 * ITEM_RING + 6];
 
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem0 = smem_base;                                 // Q sub-tile s at + s * TILE_BYTES
@@ -485,17 +500,22 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     ptx::mbar_init(s0_full, 1);
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&s1_full[s], 1);
-      ptx::mbar_init(&p_full[s], SM_WARPS);               // one arrival per softmax warp
+      ptx::mbar_init(&p_full[s], NSPLIT == 1 ? 4 : SM_WARPS);   // one arrival per softmax warp (of the sub-tile's set)
+      ptx::mbar_init(&s_taken[s], 4);
+      ptx::mbar_init(&v_done[s], 1);
       ptx::mbar_init(&o_done[s], 1);
     }
     ptx::mbar_init(drain, 1);
     ptx::mbar_init(xbar, SM_WARPS);                       // one arrival per softmax warp
-    ptx::mbar_init(l_ready, SM_WARPS);
-    ptx::mbar_init(&o_free[0], kTma ? 128 : SM_THREADS);   // whoever runs the epilogue
-    ptx::mbar_init(&o_free[1], kTma ? 128 : SM_THREADS);
+    ptx::mbar_init(l_ready, NSPLIT == 1 ? 4 : SM_WARPS);
+    ptx::mbar_init(l_ready1, 4);
+    ptx::mbar_init(pv0_done, 1);
+    ptx::mbar_init(drain2, 1);
+    ptx::mbar_init(&o_free[0], (kTma || NSPLIT == 1) ? 128 : SM_THREADS);   // whoever runs the epilogue
+    ptx::mbar_init(&o_free[1], (kTma || NSPLIT == 1) ? 128 : SM_THREADS);
     // ring consumers, one arrival per warp: softmax warps, the MMA warp, and either the four epilogue warps
     // plus the TMA thread, or the four cp.async loader warps
-    const uint32_t consumers = SM_WARPS + 1 + (kTma ? 5 : 4);
+    const uint32_t consumers = SM_WARPS + (NSPLIT == 1 ? 2 : 1) + (kTma ? 5 : 4);
     for (int r = 0; r < ITEM_RING; ++r) {
       ptx::mbar_init(&slot_ready[r], 1);
       ptx::mbar_init(&slot_free[r], consumers);
@@ -521,6 +541,15 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     ok = ptx::mbar_wait(&s1_full[(j) & 1], ((j) >> 1) & 1, abort_p);                \
     if (!ok) { if (*abort_p == 1) *abort_p = (code); }                              \
   } while (0)
+  // The V stage key tile j is to be loaded into is free: in the split forms PV1 of key tile j-2 was
+  // issued before QK1 of key tile j-1, whose signal the loaders use; in the row-owner form the PV warp
+  // signals for itself.
+#define INTRA_WAIT_V_STAGE(j, code)                                                  \
+  do {                                                                              \
+    if (NSPLIT == 1) ok = ptx::mbar_wait(&v_done[(j) & 1], (((j) - 2) >> 1) & 1, abort_p);   \
+    else ok = ptx::mbar_wait(&s1_full[((j) - 1) & 1], (((j) - 1) >> 1) & 1, abort_p); \
+    if (!ok) { if (*abort_p == 1) *abort_p = (code); }                              \
+  } while (0)
 
   // Item `seq` of this CTA's list, from the ring; leaves the loop at the end marker.
 #define INTRA_RING_ACQUIRE(sl, code)                                                 \
@@ -538,6 +567,134 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     // scheduler then hide each other's latencies while the tensor core works on the other sub-tile.
     // The parts of a row agree on the row maximum through shared memory and a bounded mbarrier.
     ptx::setmaxnreg_inc<SM_REGS>();
+    if constexpr (NSPLIT == 1) {
+      // ---- row-owner form: warps 0-3 own sub-tile 0, warps 4-7 sub-tile 1; thread = query row. Each set
+      //      runs its own loop, paced only by its own barriers. TMEM: shared score buffer cols 0-127,
+      //      P0 cols 128-191, P1 cols 192-255, O0 / O1 as in the split forms. -----------------------------
+      const int sx = warp >> 2;
+      const int row = tid & 127;
+      const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
+      const uint32_t p_addr = lane_addr + 128 + sx * 64;
+      const uint32_t o_addr = lane_addr + 256 + sx * 128;
+      const float scale_log2 = p.f.scale_log2;
+      uint32_t kt = 0;                                    // key tiles processed so far by this CTA
+      uint32_t n_done = 0;                                // items finished
+      bool ok = true;
+      for (int seq = 0; ok; ++seq) {
+        INTRA_RING_ACQUIRE(sl, 52);
+        const int n_kv = sl.n_kv;
+        const int lo = sl.lo[sx][row], hi = sl.hi[sx][row];
+        const int tk = sl.token[sx][row];
+        const int item_b = sl.b, item_h = sx ? sl.h1 : sl.h0;
+        INTRA_RING_RELEASE_WARP();
+        float m_run = -CUDART_INF_F, l_run = 0.f;
+        for (int n = 0; n < n_kv && ok; ++n, ++kt) {
+          // QK^T of this sub-tile: sub-tile 0's has a barrier of its own, sub-tile 1's is the key tile's last
+          ok = sx ? ptx::mbar_wait(&s1_full[kt & 1], (kt >> 1) & 1, abort_p) : ptx::mbar_wait(s0_full, kt & 1, abort_p);
+          if (!ok) { if (*abort_p == 1) *abort_p = 11 + sx; break; }
+          ptx::tc_fence_after();
+          float s[TILE_N];
+          uint32_t* const su = reinterpret_cast<uint32_t*>(s);
+          const int u0 = n * TILE_N;
+          float tile_max;
+          if (!__any_sync(0xffffffffu, lo > u0 || hi < u0 + TILE_N - 1)) {
+            // the row maximum of one 32-column chunk is worked out while the next chunk is on its way
+            ptx::tmem_ld32(lane_addr, su);
+            ptx::tmem_wait_ld();
+            ptx::tmem_ld32(lane_addr + 32, su + 32);
+            tile_max = sm::row_max(*reinterpret_cast<const float(*)[32]>(&s[0]));
+            ptx::tmem_wait_ld();
+            ptx::tmem_ld32(lane_addr + 64, su + 64);
+            tile_max = fmaxf(tile_max, sm::row_max(*reinterpret_cast<const float(*)[32]>(&s[32])));
+            ptx::tmem_wait_ld();
+            ptx::tmem_ld32(lane_addr + 96, su + 96);
+            tile_max = fmaxf(tile_max, sm::row_max(*reinterpret_cast<const float(*)[32]>(&s[64])));
+            ptx::tmem_wait_ld();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&s_taken[sx]);   // the other sub-tile's QK^T may overwrite the buffer
+            tile_max = fmaxf(tile_max, sm::row_max(*reinterpret_cast<const float(*)[32]>(&s[96])));
+          } else {
+#pragma unroll
+            for (int c = 0; c < TILE_N / 32; ++c) ptx::tmem_ld32(lane_addr + c * 32, su + c * 32);
+            ptx::tmem_wait_ld();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&s_taken[sx]);
+            if (lo > u0 || hi < u0 + TILE_N - 1) {          // diagonal and window-edge tiles
+#pragma unroll
+              for (int c = 0; c < TILE_N; ++c) {
+                const int u = u0 + c;
+                if (u < lo || u > hi) s[c] = -CUDART_INF_F;
+              }
+            }
+            tile_max = sm::row_max(s);
+          }
+          const float m_new = fmaxf(m_run, tile_max);
+          // The running maximum moves only when the scores outgrow it by 2^8 (see the split forms below).
+          const bool grow = (m_new - m_run) * scale_log2 > RESCALE_THRESHOLD;
+          float alpha = 1.f;
+          if (grow) {
+            alpha = ptx::ex2((m_run - m_new) * scale_log2);
+            l_run *= alpha;
+            m_run = m_new;
+          }
+          // The PV of this sub-tile's previous key tile (of this item or the one before) reads the P buffer
+          // and writes O: both may be touched only once it has completed.
+          if (kt > 0) {
+            ok = sx ? ptx::mbar_wait(&v_done[(kt - 1) & 1], ((kt - 1) >> 1) & 1, abort_p)
+                    : ptx::mbar_wait(pv0_done, (kt - 1) & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 13 + sx; break; }
+            ptx::tc_fence_after();
+          }
+          if (n > 0 && __any_sync(0xffffffffu, grow)) {   // rare once the maximum has settled
+#pragma unroll 1
+            for (int c = 0; c < HEAD_DIM / 16; ++c) {
+              uint32_t o[16];
+              ptx::tmem_ld16(o_addr + c * 16, o);
+              ptx::tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              ptx::tmem_st16(o_addr + c * 16, o);
+            }
+          }
+          const float base = (m_run == -CUDART_INF_F) ? 0.f : m_run * scale_log2;
+          sm::f2 sum[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+          for (int c2 = 0; c2 < TILE_N / 32; ++c2) {
+            uint32_t pk[16];
+            sm::exp_chunk<sm::EX2_FMA_PAIRS_NONE>(s, c2 * 32, scale_log2, base, pk, sum);
+            ptx::tmem_st16(p_addr + c2 * 16, pk);
+          }
+          l_run += sm::sum4(sum);
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&p_full[sx]);
+        }
+        if (!ok) break;
+        const int ipar = n_done & 1;
+        if (kTma) {                                       // the epilogue warps take it from here
+          xch_sum[ipar][sx][0][row] = l_run;
+          if (p.f.lse != nullptr) xch_m[ipar][sx][row] = m_run;
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(sx ? l_ready1 : l_ready);
+          ++n_done;
+          continue;
+        }
+        ok = ptx::mbar_wait(&o_done[sx], n_done & 1, abort_p);       // last PV of this item
+        if (!ok) { if (*abort_p == 1) *abort_p = 15 + sx; break; }
+        ptx::tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        if (p.f.lse != nullptr && tk >= 0)
+          p.f.lse[(int64_t(item_b) * p.f.H + item_h) * p.f.prob.S + tk] = row_lse(m_run, l_run, p.f.scale_log2);
+        __nv_bfloat16* dst = p.f.o + item_b * p.f.os.sb + int64_t(tk < 0 ? 0 : tk) * p.f.os.ss + item_h * p.f.os.sh;
+        store_o_row(o_addr, HEAD_DIM, inv, dst, tk >= 0, p.wide_stores != 0);
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&o_free[sx]);
+        ++n_done;
+      }
+    } else {
     const int half = warp >> 2;                           // which COLS columns of every score tile
     const int row = tid & 127;                            // TMEM lane == query row
     const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
@@ -634,7 +791,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
 #pragma unroll
           for (int c2 = 0; c2 < COLS / 32; ++c2) {        // 32 scores -> 16 packed columns of P
             uint32_t pk[16];
-            sm::exp_chunk(s, c2 * 32, scale_log2, base, pk, sum);
+            sm::exp_chunk<sm::EX2_FMA_PAIRS_2_OF_8>(s, c2 * 32, scale_log2, base, pk, sum);
             ptx::tmem_st16(s_addr + half * (COLS / 2) + c2 * 16, pk);
           }
           l_part[sx] += sm::sum4(sum);
@@ -687,6 +844,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       if (!ok) break;
       ++n_done;
     }
+    }  // NSPLIT > 1
   } else if (warp < SM_WARPS + 4) {
     // ================================ epilogue warps / loaders =====================================
     ptx::setmaxnreg_dec<EP_REGS>();
@@ -706,10 +864,16 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
         const int item_b = sl.b, item_h[2] = {sl.h0, sl.h1};
         INTRA_RING_RELEASE_WARP();
         const int ipar = n_done & 1;
-        ok = ptx::mbar_wait(l_ready, ipar, abort_p);
-        if (!ok) { if (*abort_p == 1) *abort_p = 41; break; }
+        if (NSPLIT > 1) {
+          ok = ptx::mbar_wait(l_ready, ipar, abort_p);
+          if (!ok) { if (*abort_p == 1) *abort_p = 41; break; }
+        }
 #pragma unroll
         for (int sx = 0; sx < 2; ++sx) {
+          if (NSPLIT == 1) {                                       // each sub-tile's warp set reports for itself
+            ok = ptx::mbar_wait(sx ? l_ready1 : l_ready, ipar, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 41; break; }
+          }
           ok = ptx::mbar_wait(&o_done[sx], ipar, abort_p);         // last PV of this item
           if (!ok) { if (*abort_p == 1) *abort_p = 42 + sx; break; }
           ptx::tc_fence_after();
@@ -782,7 +946,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
           }
           ptx::cp_async_mbar_arrive_noinc(&k_full[stage]);
           if (kc >= 2) {
-            INTRA_WAIT_TILE_DONE(kc - 1, 23);
+            INTRA_WAIT_V_STAGE(kc, 23);
             if (!ok) break;
           }
           const uint32_t vdst = v_smem0 + stage * TILE_BYTES;
@@ -844,7 +1008,16 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             ptx::mbar_arrive_expect_tx(q_full, TILE_BYTES);
             tma_fetch_box(sl.q0, sl.q0_rank4, sl.q0_text ? q_op.text_map : q_op.main_map, q_smem0, q_full);
           }
-          if (kc >= 2 || (n == 0 && n_done > 0)) {      // V stage: PV1 of key tile kc-2, issued before QK1 of kc-1
+          if (NSPLIT == 1) {                            // Q1: QK1 of the previous item's last key tile; V stage: PV1 of kc-2
+            if (n == 0 && n_done > 0) {
+              INTRA_WAIT_TILE_DONE(kc - 1, 23);
+              if (!ok) break;
+            }
+            if (kc >= 2) {
+              INTRA_WAIT_V_STAGE(kc, 26);
+              if (!ok) break;
+            }
+          } else if (kc >= 2 || (n == 0 && n_done > 0)) {   // V stage: PV1 of key tile kc-2, issued before QK1 of kc-1
             INTRA_WAIT_TILE_DONE(kc - 1, 23);
             if (!ok) break;
           }
@@ -863,7 +1036,99 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
       // ---- planner: keeps the item ring filled -------------------------------------------------------
       plan_items(p, ring, slot_ready, slot_free, cta, n_cta, lane, kTma && !kSplitKV, abort_p);
     }
-    if (warp == SM_WARPS + 4) {
+    if ((warp == SM_WARPS + 4 || warp == SM_WARPS + 7) && NSPLIT == 1) {
+      // ---- row-owner form: two issuing warps, so that neither kind of product waits for the other's
+      //      operands. Warp 4N+4 issues QK0(j) QK1(j) over the CTA's key tiles j, each into the shared
+      //      score buffer as soon as the other set has copied its scores out; warp 4N+7 issues
+      //      PV0(j) PV1(j) as the sets deliver P. Each thread's commits cover its own MMAs only. ---------
+      const uint64_t k_desc0 = tile_desc_kmajor(k_smem0), v_desc0 = tile_desc_mnmajor(v_smem0);
+      constexpr uint64_t kStageStep = TILE_BYTES >> 4;    // descriptor distance between ring stages
+      const bool qk_role = warp == SM_WARPS + 4;
+      bool ok = true;
+      uint32_t j = 0;                                     // key tiles so far, counted over the CTA
+      for (int seq = 0; ok; ++seq) {
+        INTRA_RING_ACQUIRE(sl, 56);
+        const int n_kv = sl.n_kv;
+        INTRA_RING_RELEASE_WARP();
+        if (qk_role) {
+          const uint64_t q0_desc = tile_desc_kmajor(q_smem0), q1_desc = tile_desc_kmajor(q_smem0 + TILE_BYTES);
+          for (int n = 0; n < n_kv; ++n, ++j) {
+            const int stage = j % KV_STAGES;
+            if (n == 0) {
+              ok = ptx::mbar_wait(q_full, seq & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 31; break; }
+            }
+            ok = ptx::mbar_wait(&k_full[stage], (j / KV_STAGES) & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 32; break; }
+            ptx::fence_proxy_async_smem();
+            if (j > 0) {                                  // set 1 has copied the previous key tile's scores out
+              ok = ptx::mbar_wait(&s_taken[1], (j - 1) & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 33; break; }
+            }
+            ptx::tc_fence_after();
+            if (ptx::elect_one()) {
+              issue_qk_desc(q0_desc, k_desc0 + stage * kStageStep, tmem);
+              ptx::mma_commit(s0_full);
+            }
+            __syncwarp();
+            if (n == 0) {
+              ok = ptx::mbar_wait(q1_full, seq & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 42; break; }
+              ptx::fence_proxy_async_smem();
+            }
+            ok = ptx::mbar_wait(&s_taken[0], j & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 34; break; }
+            ptx::tc_fence_after();
+            if (ptx::elect_one()) {
+              issue_qk_desc(q1_desc, k_desc0 + stage * kStageStep, tmem);
+              // set 1's scores; also: the K stage and (an item's last key tile) the Q buffers are free
+              ptx::mma_commit(&s1_full[j & 1]);
+            }
+            __syncwarp();
+          }
+        } else {
+          for (int n = 0; n < n_kv; ++n, ++j) {
+            const int stage = j % KV_STAGES;
+            ok = ptx::mbar_wait(&p_full[0], j & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 35; break; }
+            ok = ptx::mbar_wait(&v_full[stage], (j / KV_STAGES) & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 40; break; }
+            ptx::fence_proxy_async_smem();
+            if (n == 0 && seq > 0) {                      // O0 of the previous item must have been read
+              ok = ptx::mbar_wait(&o_free[0], (seq - 1) & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 37; break; }
+            }
+            ptx::tc_fence_after();
+            if (ptx::elect_one()) {
+              issue_pv_desc(tmem + 128, v_desc0 + stage * kStageStep, tmem + 256, n > 0);
+              ptx::mma_commit(pv0_done);
+              if (n == n_kv - 1) ptx::mma_commit(&o_done[0]);
+            }
+            __syncwarp();
+            ok = ptx::mbar_wait(&p_full[1], j & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 36; break; }
+            if (n == 0 && seq > 0) {
+              ok = ptx::mbar_wait(&o_free[1], (seq - 1) & 1, abort_p);
+              if (!ok) { if (*abort_p == 1) *abort_p = 38; break; }
+            }
+            ptx::tc_fence_after();
+            if (ptx::elect_one()) {
+              issue_pv_desc(tmem + 192, v_desc0 + stage * kStageStep, tmem + 384, n > 0);
+              if (n == n_kv - 1) ptx::mma_commit(&o_done[1]);
+              ptx::mma_commit(&v_done[j & 1]);            // set 1's P buffer and O1, and the V stage, are free
+            }
+            __syncwarp();
+          }
+        }
+      }
+      if (!ok) {                                          // let MMAs in flight finish before TMEM is freed
+        uint64_t* const my_drain = qk_role ? drain : drain2;
+        if (ptx::elect_one()) ptx::mma_commit(my_drain);
+        __syncwarp();
+        int dummy = 0;
+        ptx::mbar_wait(my_drain, 0, &dummy, 100);
+      }
+    } else if (warp == SM_WARPS + 4) {
       uint32_t kc = 0;                                    // key tiles issued so far
       uint32_t it0 = 0, it1 = 0;                          // PVs issued per sub-tile (p_full phases)
       const uint64_t q0_desc = tile_desc_kmajor(q_smem0), q1_desc = tile_desc_kmajor(q_smem0 + TILE_BYTES);
@@ -988,6 +1253,7 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
     }
   }
 #undef INTRA_WAIT_TILE_DONE
+#undef INTRA_WAIT_V_STAGE
 #undef INTRA_RING_ACQUIRE
 #undef INTRA_RING_RELEASE_WARP
 

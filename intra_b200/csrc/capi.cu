@@ -35,7 +35,14 @@ DeviceState g_dev[MAX_DEVICES];
 
 // Test hook (intra_b200_test_force_path): overrides of the launcher's own choice of kernel variant.
 std::atomic<int> g_force_no_tma{0};      // 1: cp.async row gathers even where TMA boxes would do
-std::atomic<int> g_force_split{0};       // 2 or 4: softmax column split; 0: the launcher decides
+// Items with at least this many key tiles on average go to the row-owner form of the kernel
+// (attn_kernel_dual.cuh); below it the 4-way column split is faster (measured: equal at 8.5 key tiles
+// per item, 18-22 % behind on window patterns with their 5 key tiles, most of them masked at an edge).
+#ifndef INTRA_ROW_OWNER_MIN_TILES
+#define INTRA_ROW_OWNER_MIN_TILES 8
+#endif
+constexpr int ROW_OWNER_MIN_TILES = INTRA_ROW_OWNER_MIN_TILES;
+std::atomic<int> g_force_split{0};       // 1 (row-owner form), 2 or 4: softmax column split; 0: the launcher decides
 
 int cuda_fail(cudaError_t e) {
   g_last_cuda_error = static_cast<int>(e);
@@ -62,6 +69,8 @@ cudaError_t opt_in_smem(K kernel, int bytes) {
 }
 cudaError_t set_kernel_attributes() {
   cudaError_t e = opt_in_smem(umma_selftest_kernel, SELFTEST_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<1, false, true>, DUAL_SMEM_BYTES);
+  if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<1, false, false>, DUAL_SMEM_BYTES);
   if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<2, false, true>, DUAL_SMEM_BYTES);
   if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<2, false, false>, DUAL_SMEM_BYTES);
   if (e == cudaSuccess) e = opt_in_smem(intra_fwd_dual_kernel<4, false, true>, DUAL_SMEM_BYTES);
@@ -272,7 +281,7 @@ int check_args(const void* q, const void* k, const void* v, void* out, int B, in
 // How the launcher splits a problem into the persistent kernel's items, and which kernel variant it
 // picks (the counterpart of the reference's MASK_SWITCH / launch templates,
 // csrc/flash_attn/src/flash_fwd_launch_template.h:401-565, :720-776).
-int plan_launch(const FwdParams& p, DualParams* d, bool* four) {
+int plan_launch(const FwdParams& p, DualParams* d, int* split) {
   d->f = p;
   d->split_kv = p.prob.kind == KIND_IMG_GATHER0 ? 1 : 0;
   d->row_pairs = (d->split_kv || (p.H / p.Hkv) % 2 != 0) ? 1 : 0;
@@ -286,14 +295,16 @@ int plan_launch(const FwdParams& p, DualParams* d, bool* four) {
                build_maps(p.prob, p.q, p.qs, p.H, p.B, true, &d->maps.q_main, &d->maps.q_text, &d->maps.k_aux) &&
                build_maps(p.prob, p.k, p.ks, p.Hkv, p.B, false, &d->maps.k_main, &d->maps.k_text, &d->maps.k_aux) &&
                build_maps(p.prob, p.v, p.vs, p.Hkv, p.B, false, &d->maps.v_main, &d->maps.v_text, &d->maps.v_aux);
-  // Softmax column split (attn_kernel_dual.cuh): 4-way for short items, 2-way for long ones.
+  // Softmax arrangement (attn_kernel_dual.cuh): 4-way column split for short items, the row-owner form
+  // for long ones that share their key tiles, the 2-way split for long items with split key lists.
   int64_t n_tiles = 0, n_kv = 0;
   for (int idx = 0; idx < d->n_pair_tiles; ++idx) {
     const int t = make_pair(p.prob, d->row_pairs, idx).kv.n_kv_tiles;
     if (t > 0) { ++n_tiles; n_kv += t; }
   }
   const int force_split = g_force_split.load();
-  *four = force_split ? force_split == 4 : (n_tiles > 0 && n_kv < 24 * n_tiles);
+  *split = force_split ? force_split : (n_tiles > 0 && n_kv < int64_t(ROW_OWNER_MIN_TILES) * n_tiles) ? 4 : 1;
+  if (*split == 1 && d->split_kv) *split = 2;
   return INTRA_OK;
 }
 
@@ -317,8 +328,8 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
   p.status = status_word;
   p.lse = lse;
   DualParams d;
-  bool four = false;
-  int rc = plan_launch(p, &d, &four);
+  int split = 0;
+  int rc = plan_launch(p, &d, &split);
   if (rc != INTRA_OK) return rc;
   const int grid = d.n_items < sm_count ? d.n_items : sm_count;     // persistent: one CTA per SM
 #define INTRA_LAUNCH_DUAL(N, SPLIT) \
@@ -326,10 +337,11 @@ int launch_fwd(const void* q, const void* k, const void* v, void* out, int B, in
     if (d.use_tma) intra_fwd_dual_kernel<N, SPLIT, true><<<grid, DualCfg<N>::THREADS, DUAL_SMEM_BYTES, st>>>(d); \
     else intra_fwd_dual_kernel<N, SPLIT, false><<<grid, DualCfg<N>::THREADS, DUAL_SMEM_BYTES, st>>>(d); \
   } while (0)
-  if (four && d.split_kv) INTRA_LAUNCH_DUAL(4, true);
-  else if (four) INTRA_LAUNCH_DUAL(4, false);
+  if (split == 4 && d.split_kv) INTRA_LAUNCH_DUAL(4, true);
+  else if (split == 4) INTRA_LAUNCH_DUAL(4, false);
   else if (d.split_kv) INTRA_LAUNCH_DUAL(2, true);
-  else INTRA_LAUNCH_DUAL(2, false);
+  else if (split == 2) INTRA_LAUNCH_DUAL(2, false);
+  else INTRA_LAUNCH_DUAL(1, false);
 #undef INTRA_LAUNCH_DUAL
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
@@ -541,7 +553,7 @@ int intra_b200_interleave_heads(const void* parts, void* out, int world, int64_t
 }
 
 int intra_b200_test_force_path(int no_tma, int softmax_split) {
-  if (softmax_split != 0 && softmax_split != 2 && softmax_split != 4) return INTRA_ERR_BAD_ARG;
+  if (softmax_split != 0 && softmax_split != 1 && softmax_split != 2 && softmax_split != 4) return INTRA_ERR_BAD_ARG;
   g_force_no_tma.store(no_tma ? 1 : 0);
   g_force_split.store(softmax_split);
   return INTRA_OK;
@@ -600,9 +612,9 @@ int intra_b200_test_tma_rows(const void* q, const void* k, const void* v, int B,
   p.status = g_dev[device].status_word;
   p.lse = nullptr;
   DualParams d;
-  bool four = false;
+  int split = 0;
   const int forced = g_force_no_tma.exchange(0);           // the maps are wanted whatever the override says
-  rc = plan_launch(p, &d, &four);
+  rc = plan_launch(p, &d, &split);
   g_force_no_tma.store(forced);
   if (rc != INTRA_OK) return rc;
   if (!d.use_tma) return INTRA_ERR_UNSUPPORTED;

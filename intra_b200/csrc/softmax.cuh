@@ -101,14 +101,16 @@ __device__ __forceinline__ void ex2_fma_pipe(float x0, float x1, float& r0, floa
   r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
-// Which of every 8 consecutive score pairs take the FMA-pipe exponential (bit i = pair i).
-#ifndef INTRA_EX2_FMA_MASK
-#define INTRA_EX2_FMA_MASK 0x88u   // pairs 3 and 7: two of eight
-#endif
+// Which of every 8 consecutive score pairs take the FMA-pipe exponential (bit i = pair i). The split
+// forms of the kernel, whose softmax warps all work on one tile in lockstep, are bound by the MUFU and
+// gain from moving two pairs of eight; the row-owner form is bound by issue slots and keeps them all
+// on the MUFU.
+constexpr uint32_t EX2_FMA_PAIRS_2_OF_8 = 0x88u;   // pairs 3 and 7
+constexpr uint32_t EX2_FMA_PAIRS_NONE = 0x00u;
 
 // p[c] = 2^(s[c] * scale_log2 - base) for 32 scores starting at s[first]; returns their 16 packed
 // bf16 pairs in pk and adds the fp32 values into the four packed partial sums.
-template <int N>
+template <uint32_t FMA_PAIRS, int N>
 __device__ __forceinline__ void exp_chunk(const float (&s)[N], int first, float scale_log2, float base,
                                           uint32_t (&pk)[16], f2 (&sum)[4]) {
   const float nbase = -base;
@@ -117,7 +119,7 @@ __device__ __forceinline__ void exp_chunk(const float (&s)[N], int first, float 
     const float x0 = fmaf(s[first + 2 * c], scale_log2, nbase);
     const float x1 = fmaf(s[first + 2 * c + 1], scale_log2, nbase);
     float p0, p1;
-    if ((INTRA_EX2_FMA_MASK >> (c & 7)) & 1u) {
+    if ((FMA_PAIRS >> (c & 7)) & 1u) {
       ex2_fma_pipe(x0, x1, p0, p1);
     } else {
       p0 = ptx::ex2(x0);

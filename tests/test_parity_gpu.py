@@ -477,12 +477,12 @@ def _launcher_choice_restored(lib):
     assert lib.intra_b200_test_force_path(0, 0) == 0
 
 
-@pytest.mark.parametrize("no_tma,split", [(0, 2), (0, 4), (1, 0), (1, 2), (1, 4)],
-                         ids=["split2", "split4", "no-tma", "no-tma-split2", "no-tma-split4"])
+@pytest.mark.parametrize("no_tma,split", [(0, 1), (0, 2), (0, 4), (1, 0), (1, 1), (1, 2), (1, 4)],
+                         ids=["row-owner", "split2", "split4", "no-tma", "no-tma-row-owner", "no-tma-split2", "no-tma-split4"])
 def test_forced_kernel_paths(lib, _launcher_choice_restored, no_tma, split):
-    """Every kernel variant the launcher can choose, forced through the library's test hook: both
-    softmax column splits for every pattern, including the combinations its heuristic never picks, and
-    the cp.async row gathers where TMA boxes would have been used."""
+    """Every kernel variant the launcher can choose, forced through the library's test hook: the
+    row-owner form and both softmax column splits for every pattern, including the combinations its
+    heuristic never picks, and the cp.async row gathers where TMA boxes would have been used."""
     from intra_b200 import intra_image_attn, intra_llm_attn
     assert lib.intra_b200_test_force_path(no_tma, split) == 0
     with torch.no_grad():
