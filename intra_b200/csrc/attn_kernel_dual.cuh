@@ -621,13 +621,14 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&s_taken[sx]);
-            if (lo > u0 || hi < u0 + TILE_N - 1) {          // diagonal and window-edge tiles
+            // Diagonal and window-edge tiles: rows whose key interval does not cover the whole tile mask the
+            // scores outside it, one unsigned compare and a select per score (with || on two signed compares
+            // it compiles to a divergent branch per score, thousands of clocks a tile). Kept apart from the
+            // common path above, which predicated selects would slow down.
+            const int first = lo - u0;
+            const unsigned span = unsigned(hi - lo);
 #pragma unroll
-              for (int c = 0; c < TILE_N; ++c) {
-                const int u = u0 + c;
-                if (u < lo || u > hi) s[c] = -CUDART_INF_F;
-              }
-            }
+            for (int c = 0; c < TILE_N; ++c) s[c] = unsigned(c - first) > span ? -CUDART_INF_F : s[c];
             tile_max = sm::row_max(s);
           }
           const float m_new = fmaxf(m_run, tile_max);
