@@ -676,6 +676,14 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
         if (!ok) break;
         const int ipar = n_done & 1;
         if (kTma) {                                       // the epilogue warps take it from here
+          // ... once they are done with this sub-tile of the item before: a set is not held back by the
+          // other set or by the PVs of an item of one key tile, so without this wait it could report two
+          // items before the epilogue warps have looked at the barrier once (and overwrite the sums of the
+          // item before the last, which they may still be reading).
+          if (n_done > 0) {
+            ok = ptx::mbar_wait(&o_free[sx], (n_done - 1) & 1, abort_p);
+            if (!ok) { if (*abort_p == 1) *abort_p = 19; break; }
+          }
           xch_sum[ipar][sx][0][row] = l_run;
           if (p.f.lse != nullptr) xch_m[ipar][sx][row] = m_run;
           __syncwarp();
@@ -806,6 +814,13 @@ __global__ void __launch_bounds__(DualCfg<NSPLIT>::THREADS, 1) intra_fwd_dual_ke
 
       // ---- row sums: publish this half's share; whoever stores O adds the two halves ----------
       const int ipar = n_done & 1;
+      if (kTma && n_done > 0) {
+        // The epilogue warps must have taken the report of the item before (they have once they hand its
+        // first accumulator back) before the barrier may complete again. The order of the MMAs makes
+        // this wait return at once in practice; it turns that timing into a guarantee.
+        ok = ptx::mbar_wait(&o_free[0], (n_done - 1) & 1, abort_p);
+        if (!ok) { if (*abort_p == 1) *abort_p = 19; break; }
+      }
       xch_sum[ipar][0][half][row] = l_part[0];
       xch_sum[ipar][1][half][row] = l_part[1];
       if (half == 0 && p.f.lse != nullptr) {              // every part of a row holds the same maximum
