@@ -46,8 +46,8 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of each workload's dominant kernel (c1 and
 # c5: Scatter G=8, c2: Gather-1, c3: image Scatter, c4: Scatter G=2), from the full-size ncu captures
 # summarised under profiles/ (a profiler cannot run inside the timed region).
-NCU_TRAFFIC_BYTES = {"c1": 50432768 + 5723136, "c2": 289953024 + 98537728, "c3": 385168640 + 90143232,
-                     "c4": 1806078000 + 240076800, "c5": 6791090000 + 507540480}
+NCU_TRAFFIC_BYTES = {"c1": 50432768 + 5723136, "c2": 279402240 + 99670016, "c3": 381974272 + 90594048,
+                     "c4": 1967612000 + 238374912, "c5": 6485108000 + 507752704}
 DEFAULT_WORKLOAD = "c5"
 
 WORKLOADS = {

@@ -498,6 +498,25 @@ def test_forced_kernel_paths(lib, _launcher_choice_restored, no_tma, split):
             assert float((lse - oracle.masked_lse(q, k, mask)).abs().max()) <= LSE_ATOL, (family, pattern)
 
 
+@pytest.mark.parametrize("split", [1, 2, 4], ids=["row-owner", "split2", "split4"])
+def test_items_of_one_key_tile_back_to_back(lib, _launcher_choice_restored, split):
+    """Scatter with 128-token groups: every item of every CTA has a single key tile, so nothing but the
+    hand-offs between the softmax warps, the MMA warps and the epilogue warps paces the pipeline from
+    item to item (the case in which a role can run furthest ahead of another). Output and log-sum-exp
+    against the oracle, and no bounded wait gave up."""
+    from intra_b200 import intra_llm_attn
+    assert lib.intra_b200_test_force_path(0, split) == 0
+    S, G = 2048, 16
+    q, k, v = oracle.make_inputs(4, S, 16, 8, seed=41, device="cuda")
+    mask = torch.from_numpy(oracle.build_mask("llm", "scatter", S, group_num=G)).cuda()
+    with torch.no_grad():
+        for _ in range(3):
+            out, lse = intra_llm_attn(q, k, v, "scatter", group_num=G, strict=False, return_lse=True)
+    _util.check_parity(out, oracle.masked_attention_fp32(q, k, v, mask), oracle.masked_attention_fp32(q, k, v.abs(), mask))
+    assert float((lse - oracle.masked_lse(q, k, mask)).abs().max()) <= LSE_ATOL
+    assert _util.device_status(lib, 0, reset=True) == 0
+
+
 def test_out_argument(lib):
     """out= writes into the caller's tensor (any layout the kernels accept) and refuses one that
     does not match."""
