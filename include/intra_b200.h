@@ -148,9 +148,17 @@ int intra_b200_test_tma_rows(const void* q, const void* k, const void* v, int B,
                              int device, void* cuda_stream);
 
 /* Test hook: overrides the launcher's choice of kernel variant for all later launches of the process:
- * no_tma != 0 forces the cp.async row gathers, softmax_split 2 or 4 forces that column split;
+ * no_tma != 0 forces the cp.async row gathers; softmax_split 1 forces the row-owner form (patterns
+ * with split key lists, i.e. Gather-0, get the 2-way split instead), 2 or 4 that column split;
  * (0, 0) restores the launcher's own choice. Replaces nothing in the reference. */
 int intra_b200_test_force_path(int no_tma, int softmax_split);
+
+/* Test hook, host arithmetic only (no GPU needed): which form of the attention kernel the launcher
+ * picks for a problem: 1 = row-owner form (items of at least 8 key tiles on average that share their
+ * key tiles), 4 = 4-way column split (shorter items), 2 = 2-way split (long items with split key
+ * lists); a negative status for arguments the entry points would refuse. The counterpart of the
+ * reference's MASK_SWITCH / launch-template choice (flash_fwd_launch_template.h:401-565). */
+int intra_b200_test_kernel_form(int family, int pattern, int S, int param, int H, int Hkv);
 
 /* Test hooks for the failure path (the reference has none). _poke_status synchronises the device and
  * overwrites its status word from the host. _wait_timeout launches a two-warp kernel in which one

@@ -42,6 +42,7 @@ SIGNATURES = {
                                       ctypes.POINTER(ctypes.c_int64), _i, _vp]),
     "intra_b200_interleave_heads": (_i, [_vp, _vp, _i, ctypes.c_int64, ctypes.c_int64, _i, _vp]),
     "intra_b200_test_force_path": (_i, [_i, _i]),
+    "intra_b200_test_kernel_form": (_i, [_i, _i, _i, _i, _i, _i]),
     "intra_b200_test_poke_status": (_i, [_i, _i]),
     "intra_b200_test_wait_timeout": (_i, [_i, _vp, _i, _vp]),
 }

@@ -281,6 +281,22 @@ int check_args(const void* q, const void* k, const void* v, void* out, int B, in
 // How the launcher splits a problem into the persistent kernel's items, and which kernel variant it
 // picks (the counterpart of the reference's MASK_SWITCH / launch templates,
 // csrc/flash_attn/src/flash_fwd_launch_template.h:401-565, :720-776).
+// Softmax arrangement (attn_kernel_dual.cuh) for a problem: 4 = 4-way column split (short items),
+// 1 = row-owner form (long items that share their key tiles), 2 = 2-way split (long items with split
+// key lists). Host arithmetic only.
+int pick_form(const Problem& prob, int row_pairs, int split_kv) {
+  const int n_pairs = n_pair_tiles(prob, row_pairs);
+  int64_t n_tiles = 0, n_kv = 0;
+  for (int idx = 0; idx < n_pairs; ++idx) {
+    const int t = make_pair(prob, row_pairs, idx).kv.n_kv_tiles;
+    if (t > 0) { ++n_tiles; n_kv += t; }
+  }
+  const int force_split = g_force_split.load();
+  int form = force_split ? force_split : (n_tiles > 0 && n_kv < int64_t(ROW_OWNER_MIN_TILES) * n_tiles) ? 4 : 1;
+  if (form == 1 && split_kv) form = 2;
+  return form;
+}
+
 int plan_launch(const FwdParams& p, DualParams* d, int* split) {
   d->f = p;
   d->split_kv = p.prob.kind == KIND_IMG_GATHER0 ? 1 : 0;
@@ -295,16 +311,7 @@ int plan_launch(const FwdParams& p, DualParams* d, int* split) {
                build_maps(p.prob, p.q, p.qs, p.H, p.B, true, &d->maps.q_main, &d->maps.q_text, &d->maps.k_aux) &&
                build_maps(p.prob, p.k, p.ks, p.Hkv, p.B, false, &d->maps.k_main, &d->maps.k_text, &d->maps.k_aux) &&
                build_maps(p.prob, p.v, p.vs, p.Hkv, p.B, false, &d->maps.v_main, &d->maps.v_text, &d->maps.v_aux);
-  // Softmax arrangement (attn_kernel_dual.cuh): 4-way column split for short items, the row-owner form
-  // for long ones that share their key tiles, the 2-way split for long items with split key lists.
-  int64_t n_tiles = 0, n_kv = 0;
-  for (int idx = 0; idx < d->n_pair_tiles; ++idx) {
-    const int t = make_pair(p.prob, d->row_pairs, idx).kv.n_kv_tiles;
-    if (t > 0) { ++n_tiles; n_kv += t; }
-  }
-  const int force_split = g_force_split.load();
-  *split = force_split ? force_split : (n_tiles > 0 && n_kv < int64_t(ROW_OWNER_MIN_TILES) * n_tiles) ? 4 : 1;
-  if (*split == 1 && d->split_kv) *split = 2;
+  *split = pick_form(p.prob, d->row_pairs, d->split_kv);
   return INTRA_OK;
 }
 
@@ -550,6 +557,16 @@ int intra_b200_interleave_heads(const void* parts, void* out, int world, int64_t
       static_cast<const uint4*>(parts), static_cast<uint4*>(out), world, rows, static_cast<int>(block_bytes / 16));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? INTRA_OK : cuda_fail(e);
+}
+
+int intra_b200_test_kernel_form(int family, int pattern, int S, int param, int H, int Hkv) {
+  if (S <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0) return INTRA_ERR_BAD_ARG;
+  Problem prob;
+  const int rc = problem_from(family, pattern, S, param, &prob);
+  if (rc != INTRA_OK) return rc;
+  const int split_kv = prob.kind == KIND_IMG_GATHER0 ? 1 : 0;
+  const int row_pairs = (split_kv || (H / Hkv) % 2 != 0) ? 1 : 0;
+  return pick_form(prob, row_pairs, split_kv);
 }
 
 int intra_b200_test_force_path(int no_tma, int softmax_split) {

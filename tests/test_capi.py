@@ -107,3 +107,31 @@ def test_helper_entry_points_reject_bad_arguments(lib):
     n = ctypes.c_int64(0)
     assert lib.intra_b200_test_tma_rows(p, p, p, 1, 256, 2, 1, None, None, None, 0, 0, 8, None, None, None, None, None,
                                         ctypes.byref(n), ctypes.byref(n), 0, None) == -1   # no strides
+
+
+def test_launcher_picks_the_kernel_form_by_item_length(lib):
+    """Host arithmetic only: long items that share their key tiles go to the row-owner form, short ones
+    (window: 5 key tiles, Gather-0: 7, S=4096) to the 4-way column split; a forced form is honoured, with
+    the 2-way split standing in for the row-owner form on split key lists."""
+    form = lib.intra_b200_test_kernel_form
+    LLM, IMG = 0, 1
+    SCATTER, GATHER1, WINDOW, GATHER0 = 0, 1, 4, 4
+    assert form(LLM, SCATTER, 4096, 8, 32, 8) == 4            # 2.5 key tiles per item
+    assert form(LLM, GATHER1, 16384, 8, 32, 8) == 1           # 8.5
+    assert form(LLM, WINDOW, 16384, 576, 32, 8) == 4
+    assert form(LLM, SCATTER, 32768, 2, 32, 8) == 1
+    assert form(LLM, SCATTER, 65536, 8, 32, 8) == 1
+    assert form(LLM, WINDOW, 65536, 576, 32, 8) == 4
+    assert form(IMG, SCATTER, 512 + 64 * 64, 64, 24, 24) == 1     # 8 key tiles
+    assert form(IMG, SCATTER, 512 + 128 * 128, 128, 24, 24) == 1  # 20
+    assert form(IMG, GATHER0, 512 + 128 * 128, 128, 24, 24) == 4  # 7, split key lists
+    assert form(LLM, SCATTER, 4096, 8, 32, 5) == -1           # heads not a multiple of KV heads
+    assert form(LLM, 7, 4096, 8, 32, 8) < 0                   # no such pattern
+    try:
+        assert lib.intra_b200_test_force_path(0, 1) == 0
+        assert form(LLM, SCATTER, 4096, 8, 32, 8) == 1
+        assert form(IMG, GATHER0, 512 + 128 * 128, 128, 24, 24) == 2
+        assert lib.intra_b200_test_force_path(0, 4) == 0
+        assert form(LLM, SCATTER, 65536, 8, 32, 8) == 4
+    finally:
+        assert lib.intra_b200_test_force_path(0, 0) == 0
